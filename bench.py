@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the FlashMoE layer forward (BASELINE config 2) on 1..N B200s.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the eager CPU arm on the box's host cores
+
+One step = one forward of the layer over one batch of synthetic tokens.  At N > 1 every rank
+runs the same per-GPU batch with replicated weights (tokens sharded, no data-path collective:
+weak scaling).  Rank 0 prints ONE JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "FlashMoE layer fwd tokens/s (H=1024,N=16384,k=64,bf16) + % of HBM roofline"
+WORKLOAD = dict(name="config2: 1x4096 tokens, H=1024, I=4096, N=16384 (128x128 keys), k=64, bf16, eval",
+                T=4096, H=1024, I=4096, N=16384, k=64, norm=False)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+L2_FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# capture summarised in profiles/ (None until a capture has been taken)
+DOMINANT_KERNEL_DRAM_BYTES = None
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_inputs(dtype):
+    """Seeded default init (torch.manual_seed(0)) and x ~ N(0,1) generated on the CPU."""
+    from flash_moe_b200 import FlashMoE, FlashMoEConfig
+
+    w = WORKLOAD
+    torch.manual_seed(0)
+    layer = FlashMoE(FlashMoEConfig(w["H"], w["I"], "silu", w["N"], w["k"], w["norm"])).to(dtype).eval()
+    x = torch.randn(1, w["T"], w["H"], generator=torch.Generator().manual_seed(1)).to(dtype)
+    return layer, x
+
+
+def cpu_reference_step(ref, x32):
+    with torch.no_grad():
+        y, _ = ref(x32)
+    return y
+
+
+def build_cpu_reference():
+    """The eager CPU arm: the oracle's restatement of the reference's pure-PyTorch module, float32
+    (on CPU the reference's bf16 eager path is slower than its fp32 one), all host threads."""
+    from oracle.flashmoe_oracle import OracleFlashMoE
+
+    w = WORKLOAD
+    torch.manual_seed(0)
+    ref = OracleFlashMoE(w["H"], w["I"], w["N"], w["k"], w["norm"]).eval()
+    x = torch.randn(1, w["T"], w["H"], generator=torch.Generator().manual_seed(1))
+    return ref, x
+
+
+def time_cpu_reference(steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ref, x = build_cpu_reference()
+    for _ in range(warmup):
+        cpu_reference_step(ref, x)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_reference_step(ref, x)
+        times.append(time.perf_counter() - t0)
+    ms = 1e3 * sum(times) / len(times)
+    return ms, cores
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ms, cores = time_cpu_reference(args.steps, args.warmup)
+    T = WORKLOAD["T"]
+    val = T / (ms / 1e3)
+    sample = f"{args.steps} full forwards of {T} tokens, float32 eager on CPU, {cores} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "arm": "oracle port of the reference's eager module on host cores"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="run the shared MLP on the main stream")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch.distributed as dist
+
+    from flash_moe_b200 import StageTimer, check_status
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    dtype = torch.bfloat16
+    layer, x_cpu = build_inputs(dtype)
+    layer = layer.to(dev)
+    if args.no_overlap:
+        layer.overlap_shared_mlp = False
+    w = WORKLOAD
+    T, H, I, N, k = w["T"], w["H"], w["I"], w["N"], w["k"]
+    x_host = x_cpu.pin_memory()
+    x_dev = x_host.to(dev, non_blocking=True)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    # ---------------- device-resident timing ----------------
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            layer(x_dev)
+        torch.cuda.synchronize()
+        check_status()
+        timers = [StageTimer() for _ in range(args.steps)]
+        for t in timers:
+            t.c_array()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        sampler = ClockSampler(local)
+        barrier()
+        sampler.start()
+        t_wall = time.perf_counter()
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)  # evict L2 between timed iterations
+            starts[i].record(stream)
+            layer(x_dev, stage_timer=timers[i])
+            ends[i].record(stream)
+        barrier()
+        wall_ms = 1e3 * (time.perf_counter() - t_wall)
+        clocks = sampler.stop()
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    ms = sum(step_ms) / len(step_ms)
+    stage_ms = {n: sum(t.elapsed_ms()[n] for t in timers) / len(timers) for n in timers[0].elapsed_ms()}
+    check_status()
+
+    # ---------------- end to end: pinned host in, pinned host out, copies inside the timed region ----
+    y_host = [torch.empty(1, T, H, dtype=dtype).pin_memory() for _ in range(2)]
+    xs = [torch.empty_like(x_dev) for _ in range(2)]
+    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    free_x = [torch.cuda.Event() for _ in range(2)]
+    got_x = [torch.cuda.Event() for _ in range(2)]
+    done_y = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_steps(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(free_x[b])
+                xs[b].copy_(x_host, non_blocking=True)
+                got_x[b].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(got_x[b])
+                y, _ = layer(xs[b])
+                free_x[b].record(s_cmp)
+                done_y[b].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_y[b])
+                y_host[b].copy_(y, non_blocking=True)
+                y.record_stream(s_out)
+
+    with torch.no_grad():
+        e2e_steps(args.warmup)
+        barrier()
+        t0 = time.perf_counter()
+        e2e_steps(args.steps)
+        barrier()
+        e2e_ms = 1e3 * (time.perf_counter() - t0) / args.steps
+    check_status()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks, peak_kind = load_peaks()
+        up_flops = 2.0 * T * (2 * I) * H
+        up_ms = stage_ms["mlp_up"]
+        achieved = up_flops / (up_ms * 1e-3) / 1e12
+        # whole-layer roofline: sum of the stage bounds (tensor pipe for the GEMMs, HBM for the rest)
+        tensor_flops = 4.0 * T * H * w_nk() + 6.0 * T * H * I
+        hbm_bytes = 2 * T * H * 2 + 4 * T * w_nk() + 4 * w_nk() * H + 6 * H * I + 4 * N * H
+        bound_ms = 1e3 * (tensor_flops / (peaks["bf16_tflops"] * 1e12) + hbm_bytes / (peaks["hbm_gbs"] * 1e9))
+        line = {
+            "metric": METRIC, "value": world * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "tokens_per_gpu": T, "parallelism": f"tokens sharded x{world}, weights replicated",
+                       "l2": "flushed between timed steps (256 MiB write)",
+                       "overlap_shared_mlp": bool(layer.overlap_shared_mlp)},
+            "stage_ms": {n: round(v, 4) for n, v in stage_ms.items()},
+            "layer_roofline": {"bound_ms": round(bound_ms, 4), "frac": round(bound_ms / ms, 4), "peaks": peak_kind},
+            "roofline": {"kernel": "gemm_tcgen05_kernel<256, SWIGLU> (shared MLP gate/up GEMM + SiLU*up epilogue)",
+                         "bound": "tensor", "achieved": round(achieved, 2), "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
+                         "traffic": DOMINANT_KERNEL_DRAM_BYTES, "peak_source": peak_kind + " (burst)"},
+            "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
+                    "d2h_bytes_per_step": y_host[0].numel() * y_host[0].element_size()},
+            "gpu_launches": layer.kernels_per_forward() * args.steps,
+            "clocks": clocks, "timed_region_wall_ms": round(wall_ms, 3),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_steps = 3
+            cpu_ms, cores = time_cpu_reference(cpu_steps, 1)
+            line["cpu_baseline"] = {
+                "value": T / (cpu_ms * 1e-3), "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": f"{cpu_steps} full forwards of {T} tokens (float32 eager oracle port; CPU bf16 is slower)"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def w_nk():
+    import math
+    return math.floor(math.sqrt(WORKLOAD["N"]))
+
+
+if __name__ == "__main__":
+    main()

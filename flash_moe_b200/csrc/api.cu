@@ -1,0 +1,284 @@
+// extern "C" entry points of libfmoe_sm100a.so (declared in include/fmoe.h) and the host-side
+// orchestration of the layer forward.
+#include "common.cuh"
+
+namespace fmoe {
+
+size_t bn_workspace_bytes(int H);
+int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, int training, float momentum, float eps,
+              int dtype, int64_t ntok, int H, float* ws, cudaStream_t stream);
+
+int device_sm_count() {
+  static int cache[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+namespace {
+
+bool is16(int dtype) { return dtype == FMOE_DTYPE_BF16 || dtype == FMOE_DTYPE_F16; }
+bool valid_dtype(int dtype) { return dtype == FMOE_DTYPE_F32 || is16(dtype); }
+
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  void* take(size_t bytes) {
+    void* p = base ? base + off : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  }
+};
+
+// fork/join events for the optional second stream, one pair per device and host thread
+struct ForkJoin {
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+ForkJoin* fork_join_events() {
+  thread_local ForkJoin ev[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ev[dev].fork == nullptr) {
+    if (cudaEventCreateWithFlags(&ev[dev].fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ev[dev].join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  }
+  return &ev[dev];
+}
+
+size_t router_front_ws(int64_t T, int H, int dtype) {
+  Carver c(nullptr);
+  c.take(static_cast<size_t>(T) * H * dtype_size(dtype));
+  c.take(bn_workspace_bytes(H));
+  return c.off;
+}
+
+int router_front(const void* x, const void* w, void* rm, void* rv, int training, float momentum, float eps,
+                 void* logits, void* logp, int dtype, int64_t T, int H, int nk, void* ws, size_t ws_bytes,
+                 int32_t* status, cudaStream_t stream) {
+  if (!valid_dtype(dtype) || T < 0 || H <= 0 || nk <= 0) return FMOE_ERR_BAD_ARG;
+  if (T == 0) return FMOE_OK;
+  if (x == nullptr || w == nullptr || logits == nullptr || logp == nullptr) return FMOE_ERR_BAD_ARG;
+  if (ws == nullptr || ws_bytes < router_front_ws(T, H, dtype)) return FMOE_ERR_WORKSPACE;
+  Carver c(ws);
+  void* xn = c.take(static_cast<size_t>(T) * H * dtype_size(dtype));
+  float* bnws = static_cast<float*>(c.take(bn_workspace_bytes(H)));
+  int rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, stream);
+  if (rc != FMOE_OK) return rc;
+  const bool tc = is16(dtype) && (H % 8 == 0) && aligned16(w);
+  if (tc && gemm_router_fused_supported(nk) && aligned16(logits) && aligned16(logp))
+    return launch_gemm_router(xn, H, 0, w, logits, logp, dtype, T, nk, H, status, stream);
+  if (tc && (2 * nk) % 8 == 0 && aligned16(logits))
+    rc = launch_gemm_add(xn, w, nullptr, logits, dtype, T, 2 * nk, H, status, stream);
+  else
+    rc = launch_simt_gemm(xn, H, w, nullptr, nullptr, logits, 2 * static_cast<int64_t>(nk), dtype, 0, T, 2 * nk, H,
+                          stream);
+  if (rc != FMOE_OK) return rc;
+  return launch_log_softmax_halves(logits, logp, dtype, T, nk, stream);
+}
+
+size_t mlp_ws(int64_t T, int I, int dtype) { return align_up(static_cast<size_t>(T) * I * dtype_size(dtype), 256); }
+
+int mlp_up(const void* x, const void* gw, const void* uw, void* h, int dtype, int64_t T, int H, int I, int32_t* status,
+           cudaStream_t stream) {
+  const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(x) && aligned16(gw) && aligned16(uw);
+  if (tc) return launch_gemm_swiglu(x, gw, uw, h, dtype, T, I, H, status, stream);
+  return launch_simt_gemm(x, H, gw, uw, nullptr, h, I, dtype, 1, T, I, H, stream);
+}
+
+int mlp_down(const void* h, const void* dw, const float* addend, void* out, int dtype, int64_t T, int H, int I,
+             int32_t* status, cudaStream_t stream) {
+  const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(dw) && aligned16(out) &&
+                  (addend == nullptr || aligned16(addend));
+  if (tc) return launch_gemm_add(h, dw, addend, out, dtype, T, H, I, status, stream);
+  return launch_simt_gemm(h, I, dw, nullptr, addend, out, H, dtype, 0, T, H, I, stream);
+}
+
+struct LayerWs {
+  void *front, *logp, *scores, *indices, *gates, *acc, *h, *expert;
+  size_t front_bytes, expert_bytes, total;
+};
+
+LayerWs carve_layer(void* ws, int64_t T, int H, int I, int64_t N, int nk, int k, int dtype) {
+  Carver c(ws);
+  LayerWs w;
+  const size_t es = dtype_size(dtype);
+  w.front_bytes = router_front_ws(T, H, dtype);
+  w.front = c.take(w.front_bytes);
+  w.logp = c.take(static_cast<size_t>(2) * T * nk * es);
+  w.scores = c.take(static_cast<size_t>(T) * k * es);
+  w.indices = c.take(static_cast<size_t>(T) * k * 8);
+  w.gates = c.take(static_cast<size_t>(T) * k * es);
+  w.acc = c.take(static_cast<size_t>(T) * H * 4);
+  w.h = c.take(static_cast<size_t>(T) * I * es);
+  w.expert_bytes = expert_workspace_bytes(T, H, N, k);
+  w.expert = c.take(w.expert_bytes);
+  w.total = c.off;
+  return w;
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" {
+
+int fmoe_version(void) { return 100; }
+
+const char* fmoe_error_string(int code) {
+  if (code < 0) return cudaGetErrorString(static_cast<cudaError_t>(-code));
+  switch (code) {
+    case FMOE_OK: return "ok";
+    case FMOE_ERR_BAD_ARG: return "bad argument";
+    case FMOE_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case FMOE_ERR_WORKSPACE: return "workspace missing or too small";
+    case FMOE_ERR_ALIGNMENT: return "pointer or row size not 16-byte aligned";
+    default: return "unknown error";
+  }
+}
+
+int fmoe_router_topk(const void* log_probs, int dtype, int64_t num_tokens, int num_keys, int top_k, void* scores,
+                     int64_t* indices, void* gates, int norm_topk_prob, fmoe_stream_t stream) {
+  return launch_router_topk(log_probs, dtype, num_tokens, num_keys, top_k, scores, indices, gates, norm_topk_prob,
+                            static_cast<cudaStream_t>(stream));
+}
+
+size_t fmoe_router_front_workspace_bytes(int64_t num_tokens, int hidden, int num_keys, int dtype) {
+  (void)num_keys;
+  if (num_tokens < 0 || hidden <= 0) return 0;
+  return router_front_ws(num_tokens, hidden, dtype);
+}
+
+int fmoe_router_front(const void* x, const void* router_weight, void* running_mean, void* running_var, int training,
+                      float momentum, float eps, void* logits, void* log_probs, int dtype, int64_t num_tokens,
+                      int hidden, int num_keys, void* workspace, size_t workspace_bytes, int32_t* status,
+                      fmoe_stream_t stream) {
+  return router_front(x, router_weight, running_mean, running_var, training, momentum, eps, logits, log_probs, dtype,
+                      num_tokens, hidden, num_keys, workspace, workspace_bytes, status,
+                      static_cast<cudaStream_t>(stream));
+}
+
+size_t fmoe_expert_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k) {
+  return expert_workspace_bytes(num_tokens, hidden, num_experts, top_k);
+}
+
+int fmoe_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
+                        void* out, int dtype, int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts,
+                        int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_expert_forward(x, down, up, indices, gates, out, dtype, out_dtype, num_tokens, hidden, num_experts,
+                               top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+size_t fmoe_mlp_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int dtype) {
+  (void)hidden;
+  if (num_tokens < 0 || intermediate <= 0) return 0;
+  return mlp_ws(num_tokens, intermediate, dtype);
+}
+
+int fmoe_mlp_forward(const void* x, const void* gate_w, const void* up_w, const void* down_w, const float* addend,
+                     void* out, int dtype, int64_t num_tokens, int hidden, int intermediate, void* workspace,
+                     size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype) || num_tokens < 0 || hidden <= 0 || intermediate <= 0) return FMOE_ERR_BAD_ARG;
+  if (num_tokens == 0) return FMOE_OK;
+  if (x == nullptr || gate_w == nullptr || up_w == nullptr || down_w == nullptr || out == nullptr)
+    return FMOE_ERR_BAD_ARG;
+  if (workspace == nullptr || workspace_bytes < mlp_ws(num_tokens, intermediate, dtype)) return FMOE_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = mlp_up(x, gate_w, up_w, workspace, dtype, num_tokens, hidden, intermediate, status, s);
+  if (rc != FMOE_OK) return rc;
+  return mlp_down(workspace, down_w, addend, out, dtype, num_tokens, hidden, intermediate, status, s);
+}
+
+size_t fmoe_layer_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int64_t num_experts, int num_keys,
+                                  int top_k, int dtype) {
+  if (num_tokens < 0 || hidden <= 0 || intermediate <= 0 || num_experts <= 0 || num_keys <= 0 || top_k < 0) return 0;
+  return carve_layer(nullptr, num_tokens, hidden, intermediate, num_experts, num_keys, top_k, dtype).total;
+}
+
+int fmoe_layer_forward(const fmoe_layer_args* a) {
+  if (a == nullptr) return FMOE_ERR_BAD_ARG;
+  const int64_t T = a->num_tokens;
+  const int H = a->hidden, I = a->intermediate, nk = a->num_keys, k = a->top_k, dtype = a->dtype;
+  const int64_t N = a->num_experts;
+  if (!valid_dtype(dtype) || T < 0 || H <= 0 || I <= 0 || N <= 0 || nk <= 0 || k < 0 || k > nk) return FMOE_ERR_BAD_ARG;
+  if (static_cast<int64_t>(nk) * nk > N) return FMOE_ERR_BAD_ARG;  // flat ids must address the tables
+  if (T == 0) return FMOE_OK;
+  if (!a->x || !a->gate_proj || !a->up_proj || !a->down_proj || !a->router_gate || !a->down_embed || !a->up_embed ||
+      !a->y || !a->router_logits)
+    return FMOE_ERR_BAD_ARG;
+  const LayerWs w = carve_layer(a->workspace, T, H, I, N, nk, k, dtype);
+  if (a->workspace == nullptr || a->workspace_bytes < w.total) return FMOE_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(a->stream);
+  cudaStream_t s2 = static_cast<cudaStream_t>(a->aux_stream);
+  int64_t* indices = a->indices_out ? a->indices_out : static_cast<int64_t*>(w.indices);
+  void* gates = a->gates_out ? a->gates_out : w.gates;
+  int rc;
+  auto mark = [&](int stage, int end, cudaStream_t st) -> int {
+    if (a->stage_events == nullptr) return FMOE_OK;
+    void* ev = a->stage_events[2 * stage + end];
+    if (ev == nullptr) return FMOE_OK;
+    FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(ev), st));
+    return FMOE_OK;
+  };
+#define FMOE_MARK(stage, end, st)                         \
+  do {                                                    \
+    if ((rc = mark(stage, end, st)) != FMOE_OK) return rc; \
+  } while (0)
+
+  // shared MLP, first half: h = silu(x Wg^T) * (x Wu^T) - independent of routing, may overlap it
+  ForkJoin* fj = nullptr;
+  if (s2 != nullptr && s2 != s) {
+    fj = fork_join_events();
+    if (fj == nullptr) return -static_cast<int>(cudaErrorUnknown);
+    FMOE_CUDA_TRY(cudaEventRecord(fj->fork, s));
+    FMOE_CUDA_TRY(cudaStreamWaitEvent(s2, fj->fork, 0));
+    FMOE_MARK(FMOE_STAGE_MLP_UP, 0, s2);
+    rc = mlp_up(a->x, a->gate_proj, a->up_proj, w.h, dtype, T, H, I, a->status, s2);
+    if (rc != FMOE_OK) return rc;
+    FMOE_MARK(FMOE_STAGE_MLP_UP, 1, s2);
+    FMOE_CUDA_TRY(cudaEventRecord(fj->join, s2));
+  }
+
+  // router: batch-norm -> sub-key GEMM -> log-softmax -> product-key top-k (+ gates)
+  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 0, s);
+  rc = router_front(a->x, a->router_gate, a->running_mean, a->running_var, a->training, a->bn_momentum, a->bn_eps,
+                    a->router_logits, w.logp, dtype, T, H, nk, w.front, w.front_bytes, a->status, s);
+  if (rc != FMOE_OK) return rc;
+  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
+  FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 0, s);
+  rc = launch_router_topk(w.logp, dtype, T, nk, k, w.scores, indices, gates, a->norm_topk_prob, s);
+  if (rc != FMOE_OK) return rc;
+  FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 1, s);
+  FMOE_MARK(FMOE_STAGE_EXPERTS, 0, s);
+
+  // routed experts into an fp32 accumulator
+  rc = launch_expert_forward(a->x, a->down_embed, a->up_embed, indices, gates, w.acc, dtype, FMOE_DTYPE_F32, T, H, N, k,
+                             w.expert, w.expert_bytes, a->status, s);
+  if (rc != FMOE_OK) return rc;
+  FMOE_MARK(FMOE_STAGE_EXPERTS, 1, s);
+
+  if (fj != nullptr) {
+    FMOE_CUDA_TRY(cudaStreamWaitEvent(s, fj->join, 0));
+  } else {
+    FMOE_MARK(FMOE_STAGE_MLP_UP, 0, s);
+    rc = mlp_up(a->x, a->gate_proj, a->up_proj, w.h, dtype, T, H, I, a->status, s);
+    if (rc != FMOE_OK) return rc;
+    FMOE_MARK(FMOE_STAGE_MLP_UP, 1, s);
+  }
+  // y = h Wd^T + experts, one rounding
+  FMOE_MARK(FMOE_STAGE_MLP_DOWN, 0, s);
+  rc = mlp_down(w.h, a->down_proj, static_cast<const float*>(w.acc), a->y, dtype, T, H, I, a->status, s);
+  if (rc != FMOE_OK) return rc;
+  FMOE_MARK(FMOE_STAGE_MLP_DOWN, 1, s);
+#undef FMOE_MARK
+  return FMOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+// Shared helpers for the FlashMoE forward kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/fmoe.h"
+
+namespace fmoe {
+
+#define FMOE_CUDA_TRY(expr)                         \
+  do {                                              \
+    cudaError_t _e = (expr);                        \
+    if (_e != cudaSuccess) return -static_cast<int>(_e); \
+  } while (0)
+
+#define FMOE_LAUNCH_CHECK()                         \
+  do {                                              \
+    cudaError_t _e = cudaGetLastError();            \
+    if (_e != cudaSuccess) return -static_cast<int>(_e); \
+  } while (0)
+
+inline int dtype_size(int dtype) { return dtype == FMOE_DTYPE_F32 ? 4 : 2; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline int next_pow2(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+int device_sm_count();  // cached per device (api.cu)
+
+// ---- scalar conversions -------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// value after one rounding to T, as float
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float silu_f32(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
+// ---- 16-byte vectors of T -----------------------------------------------------------------
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+// unpack a 16-byte register quad into floats
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& q, float (&f)[Vec16<T>::N]);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& q, float (&f)[4]) {
+  f[0] = __uint_as_float(q.x); f[1] = __uint_as_float(q.y); f[2] = __uint_as_float(q.z); f[3] = __uint_as_float(q.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& q, float (&f)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <> __device__ __forceinline__ void unpack16<__half>(const uint4& q, float (&f)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+    const float2 v = __half22float2(h);
+    f[2 * i] = v.x; f[2 * i + 1] = v.y;
+  }
+}
+
+template <typename T> __device__ __forceinline__ uint4 pack16(const float (&f)[Vec16<T>::N]);
+template <> __device__ __forceinline__ uint4 pack16<float>(const float (&f)[4]) {
+  return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <> __device__ __forceinline__ uint4 pack16<__nv_bfloat16>(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <> __device__ __forceinline__ uint4 pack16<__half>(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// ---- order-preserving float <-> uint32 map (larger float <=> larger unsigned) ---------------
+__device__ __forceinline__ uint32_t f32_to_ord(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__device__ __forceinline__ float ord_to_f32(uint32_t u) {
+  return __uint_as_float(u ^ ((u >> 31) ? 0x80000000u : 0xFFFFFFFFu));
+}
+
+// ---- internal launchers (one per .cu) -----------------------------------------------------
+int launch_router_topk(const void* log_probs, int dtype, int64_t T, int nk, int k, void* scores, int64_t* indices,
+                       void* gates, int norm, cudaStream_t stream);
+
+size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k);
+int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
+                          void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream);
+
+// C[M,N] = A[M,K] * B[N,K]^T on tcgen05 with a fused epilogue (gemm_sm100.cu); bf16/fp16 only.
+int launch_gemm_swiglu(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I, int K,
+                       int32_t* status, cudaStream_t stream);
+int launch_gemm_add(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N, int K,
+                    int32_t* status, cudaStream_t stream);
+// router: per half h: logits[:, h*nk:(h+1)*nk] = A[:, h*a_half_koff : +K] * W[h*nk:(h+1)*nk, :K]^T, then log-softmax
+int launch_gemm_router(const void* xn, int64_t a_cols, int a_half_koff, const void* w, void* logits, void* log_probs,
+                       int dtype, int64_t M, int nk, int K, int32_t* status, cudaStream_t stream);
+bool gemm_router_fused_supported(int nk);
+
+// fp32-FMA GEMM on CUDA cores (simt_gemm.cu): float32 modules and shapes TMA cannot address.
+int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1, const float* addend, void* out,
+                     int64_t ldo, int dtype, int swiglu, int64_t M, int N, int K, cudaStream_t stream);
+
+// elementwise.cu
+int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, int64_t T, int nk, cudaStream_t stream);
+
+}  // namespace fmoe

@@ -1,0 +1,172 @@
+// Small memory-bound stages of the router front end:
+//   batch-norm (affine=False) statistics / normalisation  (flash_moe/modules/flash_moe.py:49,:65)
+//   per-half log-softmax of the router logits              (flash_moe/modules/flash_moe.py:72)
+#include "common.cuh"
+
+namespace fmoe {
+namespace {
+
+constexpr unsigned kFull = 0xFFFFFFFFu;
+constexpr int kBnSplits = 32;  // row splits of the statistics pass (fixed => deterministic sums)
+
+// partial[s][c] = sum over the rows of split s of x[r][c]; same for squares.
+template <typename T>
+__global__ void bn_partial_kernel(const T* __restrict__ x, int64_t ntok, int H, float* __restrict__ psum,
+                                  float* __restrict__ psq) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  if (c >= H) return;
+  const int64_t rows_per = (ntok + kBnSplits - 1) / kBnSplits;
+  const int64_t r0 = s * rows_per;
+  const int64_t r1 = r0 + rows_per < ntok ? r0 + rows_per : ntok;
+  float a = 0.f, b = 0.f;
+  for (int64_t r = r0; r < r1; ++r) {
+    const float v = to_f32<T>(x[r * H + c]);
+    a += v;
+    b = fmaf(v, v, b);
+  }
+  psum[static_cast<int64_t>(s) * H + c] = a;
+  psq[static_cast<int64_t>(s) * H + c] = b;
+}
+
+// mean / inverse std per feature.  Training: from the batch partials (biased variance) and the
+// running buffers are updated (momentum, unbiased variance).  Eval: from the running buffers.
+template <typename T>
+__global__ void bn_finalize_kernel(const float* __restrict__ psum, const float* __restrict__ psq, T* running_mean,
+                                   T* running_var, int training, float momentum, float eps, int64_t ntok, int H,
+                                   float* __restrict__ mean_out, float* __restrict__ invstd_out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float mean, var;
+  if (training) {
+    double s = 0.0, q = 0.0;
+    for (int i = 0; i < kBnSplits; ++i) {
+      s += static_cast<double>(psum[static_cast<int64_t>(i) * H + c]);
+      q += static_cast<double>(psq[static_cast<int64_t>(i) * H + c]);
+    }
+    const double m = s / static_cast<double>(ntok);
+    double v = q / static_cast<double>(ntok) - m * m;
+    if (v < 0.0) v = 0.0;
+    mean = static_cast<float>(m);
+    var = static_cast<float>(v);
+    if (running_mean != nullptr && running_var != nullptr) {
+      const double unbiased = ntok > 1 ? v * static_cast<double>(ntok) / static_cast<double>(ntok - 1) : v;
+      const float rm = to_f32<T>(running_mean[c]);
+      const float rv = to_f32<T>(running_var[c]);
+      running_mean[c] = from_f32<T>((1.f - momentum) * rm + momentum * mean);
+      running_var[c] = from_f32<T>((1.f - momentum) * rv + momentum * static_cast<float>(unbiased));
+    }
+  } else {
+    mean = to_f32<T>(running_mean[c]);
+    var = to_f32<T>(running_var[c]);
+  }
+  mean_out[c] = mean;
+  invstd_out[c] = 1.0f / sqrtf(var + eps);
+}
+
+template <typename T>
+__global__ void bn_apply_kernel(const T* __restrict__ x, T* __restrict__ xn, const float* __restrict__ mean,
+                                const float* __restrict__ invstd, int64_t ntok, int H) {
+  constexpr int VEC = Vec16<T>::N;
+  const int64_t nvec = ntok * H / VEC;
+  const int hv = H / VEC;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c0 = static_cast<int>(i % hv) * VEC;
+    float f[VEC];
+    unpack16<T>(ldg16(x + i * VEC), f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f[j] = (f[j] - __ldg(mean + c0 + j)) * __ldg(invstd + c0 + j);
+    *reinterpret_cast<uint4*>(xn + i * VEC) = pack16<T>(f);
+  }
+}
+
+// one warp per (token, half): lp = (l - max) - log(sum exp(l - max)), rounded to T
+template <typename T>
+__global__ void log_softmax_halves_kernel(const T* __restrict__ logits, T* __restrict__ logp, int64_t ntok, int nk) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  for (int64_t task = warp_global; task < 2 * ntok; task += warps_total) {
+    const int64_t t = task >> 1;
+    const int h = static_cast<int>(task & 1);
+    const T* src = logits + t * 2 * nk + static_cast<int64_t>(h) * nk;
+    T* dst = logp + (static_cast<int64_t>(h) * ntok + t) * nk;
+    float vmax = -INFINITY;
+    for (int i = lane; i < nk; i += 32) vmax = fmaxf(vmax, to_f32<T>(src[i]));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(kFull, vmax, d));
+    float vsum = 0.f;
+    for (int i = lane; i < nk; i += 32) vsum += expf(to_f32<T>(src[i]) - vmax);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) vsum += __shfl_xor_sync(kFull, vsum, d);
+    const float lsum = logf(vsum);
+    for (int i = lane; i < nk; i += 32) dst[i] = from_f32<T>((to_f32<T>(src[i]) - vmax) - lsum);
+  }
+}
+
+template <typename T>
+int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float momentum, float eps, int64_t ntok, int H,
+             float* ws, cudaStream_t stream) {
+  float* psum = ws;
+  float* psq = ws + static_cast<size_t>(kBnSplits) * H;
+  float* mean = psq + static_cast<size_t>(kBnSplits) * H;
+  float* invstd = mean + H;
+  if (training) {
+    dim3 grid((H + 127) / 128, kBnSplits);
+    bn_partial_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), ntok, H, psum, psq);
+    FMOE_LAUNCH_CHECK();
+  }
+  bn_finalize_kernel<T><<<(H + 127) / 128, 128, 0, stream>>>(psum, psq, static_cast<T*>(rm), static_cast<T*>(rv),
+                                                            training, momentum, eps, ntok, H, mean, invstd);
+  FMOE_LAUNCH_CHECK();
+  constexpr int VEC = Vec16<T>::N;
+  const int64_t nvec = ntok * H / VEC;
+  const int64_t want = (nvec + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  bn_apply_kernel<T><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+      static_cast<const T*>(x), static_cast<T*>(xn), mean, invstd, ntok, H);
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+}  // namespace
+
+size_t bn_workspace_bytes(int H) { return static_cast<size_t>(2 * kBnSplits + 2) * H * sizeof(float); }
+
+int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, int training, float momentum, float eps,
+              int dtype, int64_t ntok, int H, float* ws, cudaStream_t stream) {
+  if (x == nullptr || xn == nullptr || ws == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
+  if (!training && (running_mean == nullptr || running_var == nullptr)) return FMOE_ERR_BAD_ARG;
+  if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(x) || !aligned16(xn)) return FMOE_ERR_ALIGNMENT;
+  switch (dtype) {
+    case FMOE_DTYPE_F32: return bn_typed<float>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
+    case FMOE_DTYPE_BF16: return bn_typed<__nv_bfloat16>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
+    case FMOE_DTYPE_F16: return bn_typed<__half>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
+    default: return FMOE_ERR_BAD_ARG;
+  }
+}
+
+int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, int64_t ntok, int nk,
+                              cudaStream_t stream) {
+  if (logits == nullptr || log_probs == nullptr || ntok <= 0 || nk <= 0) return FMOE_ERR_BAD_ARG;
+  const int64_t want = (2 * ntok + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  switch (dtype) {
+    case FMOE_DTYPE_F32:
+      log_softmax_halves_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(logits), static_cast<float*>(log_probs), ntok, nk);
+      break;
+    case FMOE_DTYPE_BF16:
+      log_softmax_halves_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), static_cast<__nv_bfloat16*>(log_probs), ntok, nk);
+      break;
+    case FMOE_DTYPE_F16:
+      log_softmax_halves_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(logits), static_cast<__half*>(log_probs), ntok, nk);
+      break;
+    default: return FMOE_ERR_BAD_ARG;
+  }
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+}  // namespace fmoe

@@ -1,0 +1,459 @@
+// Fine-grained expert forward for sm_100a:
+//   out[t] = sum_j silu(<x[t], D[e_tj]>) * g[t,j] * U[e_tj]
+// (flash_moe/ops/triton/flash_expert.py:13-211, preprocessing :528-577).
+//
+// Schedule
+//   1. expert-centric order of the (token, slot) pairs by a device-side counting sort
+//      (histogram with warp-aggregated atomics -> exclusive scan -> scatter); no host sync,
+//      ids outside [0, N) are dropped and flagged;
+//   2. scores pass over the SORTED pairs: a warp walks a contiguous run of pairs, keeps the
+//      current expert's down row in registers (loaded once per run of equal ids with 128-bit
+//      loads), gathers each pair's x row, reduces the dot product in fp32 and stores
+//      gs = silu(s) * gate at the pair's original (token, slot) position (4 bytes per pair);
+//      empty experts cost nothing and a hot expert is split over many warps;
+//   3. accumulate pass per token: out[t] = sum_j gs[t,j] * U[e_tj] in fp32 registers, fixed
+//      slot order, one rounding on store - no atomics, run-to-run deterministic.
+#include "common.cuh"
+
+namespace fmoe {
+namespace {
+
+constexpr unsigned kFull = 0xFFFFFFFFu;
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+// ---------------------------------------------------------------- 1. counting sort
+__global__ void expert_hist_kernel(const int64_t* __restrict__ idx, int64_t P, int64_t N, int* __restrict__ counts,
+                                   int* __restrict__ rank, int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  bool bad = false;
+  for (int64_t base = warp_global * 32; base < P; base += warps_total * 32) {
+    const int64_t p = base + lane;
+    int64_t e = -1;
+    if (p < P) e = idx[p];
+    const bool valid = (p < P) && (e >= 0) && (e < N);
+    if (p < P && !valid) bad = true;
+    // lanes holding the same expert id share one atomic; invalid lanes get distinct keys
+    const unsigned key = valid ? static_cast<unsigned>(e) : (0x80000000u | lane);
+    const unsigned peers = __match_any_sync(kFull, key);
+    const int leader = __ffs(peers) - 1;
+    int basecnt = 0;
+    if (valid && lane == leader) basecnt = atomicAdd(&counts[e], __popc(peers));
+    basecnt = __shfl_sync(kFull, basecnt, leader);
+    if (p < P) rank[p] = valid ? basecnt + __popc(peers & ((1u << lane) - 1u)) : -1;
+  }
+  if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_EXPERT_ID);
+}
+
+__device__ __forceinline__ int block_reduce_sum(int v, int* sh) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(kFull, v, d);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  int tot = 0;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += sh[w];
+  __syncthreads();
+  return tot;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_tile_sums_kernel(const int* __restrict__ counts, int64_t N,
+                                                                     int* __restrict__ tile_sums) {
+  __shared__ int sh[kScanThreads / 32];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile;
+  int v = 0;
+  for (int i = threadIdx.x; i < kScanTile; i += kScanThreads)
+    if (base + i < N) v += counts[base + i];
+  const int tot = block_reduce_sum(v, sh);
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = tot;
+}
+
+// offsets[i] = sum(counts[0..i)), offsets[N] = total.  tile_sums == nullptr: the prefix of the
+// preceding tiles is recomputed from counts (cheap when there are only a few tiles).
+__global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(const int* __restrict__ counts, int64_t N,
+                                                                  const int* __restrict__ tile_sums,
+                                                                  int* __restrict__ offsets) {
+  __shared__ int sh[kScanThreads / 32];
+  __shared__ int warp_pref[kScanThreads / 32];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile;
+  int v = 0;
+  if (tile_sums != nullptr) {
+    for (int i = threadIdx.x; i < static_cast<int>(blockIdx.x); i += kScanThreads) v += tile_sums[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < base; i += kScanThreads) v += counts[i];
+  }
+  const int prefix = block_reduce_sum(v, sh);
+
+  int item[kScanItems];
+  int tsum = 0;
+  const int64_t first = base + static_cast<int64_t>(threadIdx.x) * kScanItems;
+#pragma unroll
+  for (int i = 0; i < kScanItems; ++i) {
+    item[i] = (first + i < N) ? counts[first + i] : 0;
+    tsum += item[i];
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = tsum;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(kFull, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) warp_pref[warp] = incl;
+  __syncthreads();
+  int wbase = 0;
+  for (int w = 0; w < warp; ++w) wbase += warp_pref[w];
+  int run = prefix + wbase + incl - tsum;
+#pragma unroll
+  for (int i = 0; i < kScanItems; ++i) {
+    if (first + i < N) offsets[first + i] = run;
+    run += item[i];
+    if (first + i == N - 1) offsets[N] = run;
+  }
+}
+
+__global__ void expert_scatter_kernel(const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                                      const int* __restrict__ offsets, int64_t P, int* __restrict__ sorted_pair,
+                                      int* __restrict__ sorted_expert) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < P;
+       p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int r = rank[p];
+    if (r < 0) continue;
+    const int e = static_cast<int>(idx[p]);
+    const int pos = offsets[e] + r;
+    sorted_pair[pos] = static_cast<int>(p);
+    sorted_expert[pos] = e;
+  }
+}
+
+// ---------------------------------------------------------------- 2. scores over sorted pairs
+// NCH > 0: the row fits NCH 16-byte chunks per lane and the down row is cached in registers.
+// NCH == 0: any H, the down row is re-read (L1-resident) for every pair.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict__ x, const T* __restrict__ down,
+                                                           const int* __restrict__ sorted_pair,
+                                                           const int* __restrict__ sorted_expert,
+                                                           const int* __restrict__ total_ptr,
+                                                           const T* __restrict__ gates, float* __restrict__ gs, int H,
+                                                           int k, int chunk) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int R = NCH > 0 ? NCH : 1;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int total = *total_ptr;
+
+  for (int64_t task = warp_global; task * chunk < total; task += warps_total) {
+    const int pos0 = static_cast<int>(task * chunk);
+    const int pos1 = min(pos0 + chunk, total);
+    int cur_e = -1;
+    float dreg[R][VEC];
+    uint4 xq[R], xn[R];
+    // prefetch the first pair's x row
+    int p_next = sorted_pair[pos0];
+    if (NCH > 0) {
+      const T* xr = x + static_cast<int64_t>(p_next / k) * H;
+#pragma unroll
+      for (int c = 0; c < R; ++c) {
+        const int col = (c * 32 + lane) * VEC;
+        xn[c] = (col < H) ? ldg16(xr + col) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    for (int pos = pos0; pos < pos1; ++pos) {
+      const int p = p_next;
+      const int e = sorted_expert[pos];
+      float acc = 0.f;
+      if (NCH > 0) {
+#pragma unroll
+        for (int c = 0; c < R; ++c) xq[c] = xn[c];
+        if (pos + 1 < pos1) {  // issue the next pair's gather before the math of this one
+          p_next = sorted_pair[pos + 1];
+          const T* xr = x + static_cast<int64_t>(p_next / k) * H;
+#pragma unroll
+          for (int c = 0; c < R; ++c) {
+            const int col = (c * 32 + lane) * VEC;
+            xn[c] = (col < H) ? ldg16(xr + col) : make_uint4(0, 0, 0, 0);
+          }
+        }
+        if (e != cur_e) {  // warp-uniform
+          cur_e = e;
+          const T* dr = down + static_cast<int64_t>(e) * H;
+#pragma unroll
+          for (int c = 0; c < R; ++c) {
+            const int col = (c * 32 + lane) * VEC;
+            const uint4 q = (col < H) ? ldg16(dr + col) : make_uint4(0, 0, 0, 0);
+            unpack16<T>(q, dreg[c]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < R; ++c) {
+          float xf[VEC];
+          unpack16<T>(xq[c], xf);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc = fmaf(xf[i], dreg[c][i], acc);
+        }
+      } else {
+        if (pos + 1 < pos1) p_next = sorted_pair[pos + 1];
+        const T* xr = x + static_cast<int64_t>(p / k) * H;
+        const T* dr = down + static_cast<int64_t>(e) * H;
+        for (int col = lane * VEC; col < H; col += 32 * VEC) {
+          float xf[VEC], df[VEC];
+          unpack16<T>(ldg16(xr + col), xf);
+          unpack16<T>(ldg16(dr + col), df);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc = fmaf(xf[i], df[i], acc);
+        }
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFull, acc, d);
+      if (lane == 0) gs[p] = silu_f32(acc) * to_f32<T>(gates[p]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- 3. per-token accumulate
+// One warp per (token, column block of 32*VEC*NCH elements).
+template <typename T, typename OutT, int NCH>
+__global__ void __launch_bounds__(256) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
+                                                          const float* __restrict__ gs, OutT* __restrict__ out,
+                                                          int64_t ntok, int H, int64_t N, int k, int colblocks) {
+  constexpr int VEC = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t tasks = ntok * colblocks;
+  for (int64_t task = warp_global; task < tasks; task += warps_total) {
+    const int64_t t = task / colblocks;
+    const int cb = static_cast<int>(task - t * colblocks);
+    const int col0 = cb * (32 * VEC * NCH);
+    float acc[NCH][VEC];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
+
+    for (int j0 = 0; j0 < k; j0 += 32) {
+      // each lane fetches one slot's (expert id, weight); invalid ids get weight 0
+      const int j = j0 + lane;
+      int64_t e_l = 0;
+      float w_l = 0.f;
+      if (j < k) {
+        e_l = idx[t * k + j];
+        w_l = gs[t * k + j];
+        if (e_l < 0 || e_l >= N) { e_l = 0; w_l = 0.f; }
+      }
+      const int nslots = min(32, k - j0);
+      int s = 0;
+      for (; s + 2 <= nslots; s += 2) {  // two gathered rows in flight
+        const int64_t e0 = __shfl_sync(kFull, e_l, s), e1 = __shfl_sync(kFull, e_l, s + 1);
+        const float w0 = __shfl_sync(kFull, w_l, s), w1 = __shfl_sync(kFull, w_l, s + 1);
+        const T* u0 = up + e0 * H + col0;
+        const T* u1 = up + e1 * H + col0;
+        uint4 q0[NCH], q1[NCH];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int col = (c * 32 + lane) * VEC;
+          const bool in = col0 + col < H;
+          q0[c] = in ? ldg16(u0 + col) : make_uint4(0, 0, 0, 0);
+          q1[c] = in ? ldg16(u1 + col) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          float f0[VEC], f1[VEC];
+          unpack16<T>(q0[c], f0);
+          unpack16<T>(q1[c], f1);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w0, f0[i], acc[c][i]);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w1, f1[i], acc[c][i]);
+        }
+      }
+      for (; s < nslots; ++s) {
+        const int64_t e0 = __shfl_sync(kFull, e_l, s);
+        const float w0 = __shfl_sync(kFull, w_l, s);
+        const T* u0 = up + e0 * H + col0;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int col = (c * 32 + lane) * VEC;
+          if (col0 + col < H) {
+            float f0[VEC];
+            unpack16<T>(ldg16(u0 + col), f0);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w0, f0[i], acc[c][i]);
+          }
+        }
+      }
+    }
+    OutT* orow = out + t * H + col0;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * VEC;
+      if (col0 + col < H) {
+        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+          for (int i = 0; i < VEC; i += 4)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + col + i) =
+                make_float4(acc[c][i], acc[c][i + 1], acc[c][i + 2], acc[c][i + 3]);
+        } else {
+          *reinterpret_cast<uint4*>(orow + col) = pack16<OutT>(acc[c]);
+        }
+      }
+    }
+  }
+}
+
+struct ExpertWs {
+  int* counts;
+  int* offsets;
+  int* tile_sums;
+  int* rank;
+  int* sorted_pair;
+  int* sorted_expert;
+  float* gs;
+  size_t bytes;
+};
+
+ExpertWs carve(void* ws, int64_t T, int64_t N, int k) {
+  const int64_t P = T * k;
+  const int64_t ntiles = (N + kScanTile - 1) / kScanTile;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void* p = ws ? static_cast<char*>(ws) + off : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  };
+  ExpertWs w;
+  w.counts = static_cast<int*>(take(static_cast<size_t>(N) * 4));
+  w.offsets = static_cast<int*>(take(static_cast<size_t>(N + 1) * 4));
+  w.tile_sums = static_cast<int*>(take(static_cast<size_t>(ntiles) * 4));
+  w.rank = static_cast<int*>(take(static_cast<size_t>(P) * 4));
+  w.sorted_pair = static_cast<int*>(take(static_cast<size_t>(P) * 4));
+  w.sorted_expert = static_cast<int*>(take(static_cast<size_t>(P) * 4));
+  w.gs = static_cast<float*>(take(static_cast<size_t>(P) * 4));
+  w.bytes = off;
+  return w;
+}
+
+template <typename T, int NCH>
+void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N, const void* gates, int H, int k,
+                   int64_t P, cudaStream_t stream) {
+  const int chunk = 16;
+  const int64_t tasks = (P + chunk - 1) / chunk;
+  const int64_t want = (tasks + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+  expert_scores_kernel<T, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down),
+                                                         w.sorted_pair, w.sorted_expert, w.offsets + N,
+                                                         static_cast<const T*>(gates), w.gs, H, k, chunk);
+}
+
+template <typename T, typename OutT, int NCH>
+void launch_accum(const void* up, const int64_t* idx, const ExpertWs& w, void* out, int64_t T_, int H, int64_t N, int k,
+                  cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  const int colblocks = (H + 32 * VEC * NCH - 1) / (32 * VEC * NCH);
+  const int64_t tasks = T_ * colblocks;
+  const int64_t want = (tasks + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+  expert_accum_kernel<T, OutT, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(up), idx, w.gs,
+                                                              static_cast<OutT*>(out), T_, H, N, k, colblocks);
+}
+
+template <typename T>
+int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
+              int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
+              cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  const int64_t P = T_ * k;
+  const int sms = device_sm_count();
+  FMOE_CUDA_TRY(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(N) * 4, stream));
+  {
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_hist_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.counts, w.rank, status);
+    FMOE_LAUNCH_CHECK();
+  }
+  {
+    const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
+    if (ntiles > 16) {
+      scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums);
+      FMOE_LAUNCH_CHECK();
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums, w.offsets);
+    } else {
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, nullptr, w.offsets);
+    }
+    FMOE_LAUNCH_CHECK();
+  }
+  {
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_scatter_kernel<<<grid, 256, 0, stream>>>(idx, w.rank, w.offsets, P, w.sorted_pair, w.sorted_expert);
+    FMOE_LAUNCH_CHECK();
+  }
+  const int per_chunk = 32 * VEC;
+  const int need = (H + per_chunk - 1) / per_chunk;
+  if (need <= 1) launch_scores<T, 1>(x, down, w, N, gates, H, k, P, stream);
+  else if (need <= 2) launch_scores<T, 2>(x, down, w, N, gates, H, k, P, stream);
+  else if (need <= 4) launch_scores<T, 4>(x, down, w, N, gates, H, k, P, stream);
+  else if (need <= 8) launch_scores<T, 8>(x, down, w, N, gates, H, k, P, stream);
+  else launch_scores<T, 0>(x, down, w, N, gates, H, k, P, stream);
+  FMOE_LAUNCH_CHECK();
+
+#define FMOE_ACCUM(NCH_)                                                                       \
+  do {                                                                                         \
+    if (out_f32) launch_accum<T, float, NCH_>(up, idx, w, out, T_, H, N, k, stream);           \
+    else launch_accum<T, T, NCH_>(up, idx, w, out, T_, H, N, k, stream);                       \
+  } while (0)
+  if (need <= 1) FMOE_ACCUM(1);
+  else if (need <= 2) FMOE_ACCUM(2);
+  else if (need <= 4) FMOE_ACCUM(4);
+  else FMOE_ACCUM(8);
+#undef FMOE_ACCUM
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+}  // namespace
+
+size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k) {
+  (void)H;
+  if (T < 0 || N < 0 || k < 0) return 0;
+  return carve(nullptr, T, N, k).bytes;
+}
+
+int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
+                          void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+  if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
+  if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
+  if (T == 0) return FMOE_OK;
+  if (x == nullptr || down == nullptr || up == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
+  if (k > 0 && (indices == nullptr || gates == nullptr)) return FMOE_ERR_BAD_ARG;
+  if (N > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
+  const int vec = 16 / dtype_size(dtype);
+  if (H % vec != 0) return FMOE_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(down) || !aligned16(up) || !aligned16(out)) return FMOE_ERR_ALIGNMENT;
+  if (k == 0) {
+    FMOE_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(T) * H * dtype_size(out_dtype), stream));
+    return FMOE_OK;
+  }
+  const ExpertWs w = carve(ws, T, N, k);
+  if (ws == nullptr || ws_bytes < w.bytes) return FMOE_ERR_WORKSPACE;
+  const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
+  switch (dtype) {
+    case FMOE_DTYPE_F32:
+      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream);
+    case FMOE_DTYPE_BF16:
+      return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream);
+    case FMOE_DTYPE_F16:
+      return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream);
+    default:
+      return FMOE_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace fmoe

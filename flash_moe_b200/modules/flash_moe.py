@@ -1,0 +1,195 @@
+"""`FlashMoE` / `FlashMoEConfig` with the reference's API (flash_moe/modules/flash_moe.py:12-105),
+forward running on the sm_100a kernels of libfmoe_sm100a.so.
+
+Parameter and buffer names, shapes and construction order are the reference's, so a reference
+``state_dict`` loads unchanged and a common ``torch.manual_seed`` yields identical weights.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import warnings
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import _lib
+
+
+class FlashMoEConfig:
+    """Same six fields and defaults as the reference (flash_moe/modules/flash_moe.py:12-27)."""
+
+    def __init__(
+        self,
+        hidden_size: int,
+        intermediate_size: int,
+        hidden_act: str,
+        num_experts: int,
+        num_experts_per_tok: int,
+        norm_topk_prob: bool = False,
+    ):
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.hidden_act = hidden_act
+        self.num_experts = num_experts
+        self.num_experts_per_tok = num_experts_per_tok
+        self.norm_topk_prob = norm_topk_prob
+
+
+class StageTimer:
+    """CUDA events recorded by the library around each stage of one layer forward."""
+
+    def __init__(self):
+        self.events = [torch.cuda.Event(enable_timing=True) for _ in range(2 * _lib.NUM_STAGES)]
+        self._arr = (ctypes.c_void_p * (2 * _lib.NUM_STAGES))()
+        self._bound = False
+
+    def c_array(self):
+        if not self._bound:
+            # torch creates the underlying cudaEvent lazily on first record
+            s = torch.cuda.current_stream()
+            for e in self.events:
+                e.record(s)
+            for i, e in enumerate(self.events):
+                self._arr[i] = e.cuda_event
+            self._bound = True
+        return ctypes.cast(self._arr, ctypes.POINTER(ctypes.c_void_p))
+
+    def elapsed_ms(self) -> Dict[str, float]:
+        """Call after synchronising; duration of every stage of the last timed forward."""
+        return {
+            name: self.events[2 * i].elapsed_time(self.events[2 * i + 1]) for i, name in enumerate(_lib.STAGE_NAMES)
+        }
+
+
+class FlashMoE(nn.Module):
+    def __init__(self, config: FlashMoEConfig, overlap_shared_mlp: bool = True):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.intermediate_size = config.intermediate_size
+        if config.hidden_act != "silu":
+            # the reference builds act_fn from hidden_act but its kernels always apply SiLU
+            # (flash_expert.py:8-10, flash_mlp.py:8-10); same here, but say so
+            warnings.warn(f"hidden_act={config.hidden_act!r} is ignored: the FlashMoE kernels apply SiLU")
+        self.hidden_act = config.hidden_act
+
+        self.num_experts = config.num_experts
+        self.num_keys = math.floor(math.sqrt(self.num_experts))
+        self.top_k = config.num_experts_per_tok
+        self.norm_topk_prob = config.norm_topk_prob
+
+        # shared expert
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+        # router
+        self.router_gate = nn.Linear(self.hidden_size, self.num_keys * 2, bias=False)
+        self.router_norm = nn.BatchNorm1d(self.hidden_size, affine=False)
+        # routed experts
+        self.down_embed = nn.Embedding(self.num_experts, self.hidden_size)
+        self.up_embed = nn.Embedding(self.num_experts, self.hidden_size)
+
+        self.overlap_shared_mlp = overlap_shared_mlp
+        self._aux_streams: Dict[int, torch.cuda.Stream] = {}
+        self.last_indices: Optional[torch.Tensor] = None
+        self.last_gates: Optional[torch.Tensor] = None
+
+    def _aux_stream(self, dev: torch.device) -> torch.cuda.Stream:
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        if key not in self._aux_streams:
+            self._aux_streams[key] = torch.cuda.Stream(device=dev)
+        return self._aux_streams[key]
+
+    def kernels_per_forward(self) -> int:
+        """Kernels of this library launched by one forward in eval mode (16-bit dtypes, fused router
+        epilogue): batch-norm finalize + apply, router GEMM, top-k, expert histogram / scan / scatter /
+        scores / accumulate, MLP up GEMM, MLP down GEMM."""
+        n = 2 + 1 + 1 + 5 + 1 + 1
+        if self.num_keys > 256:
+            n += 1  # separate log-softmax pass
+        if (self.num_experts + 2047) // 2048 > 16:
+            n += 1  # two-level scan
+        if self.training:
+            n += 1  # batch statistics pass
+        return n
+
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        return_routing: bool = False,
+        stage_timer: Optional[StageTimer] = None,
+        **kwargs,
+    ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(y[B,S,H], router_logits[2, B*S, num_keys]) like the reference; forward only.
+
+        ``return_routing=True`` additionally keeps the selected expert ids and gates in
+        ``self.last_indices`` / ``self.last_gates``.
+        """
+        bsz, seq_len, _ = hidden_states.shape
+        dev = _lib.require_cuda(hidden_states)
+        x = hidden_states.reshape(-1, self.hidden_size)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        dtype = x.dtype
+        w = self.gate_proj.weight
+        if w.dtype != dtype or w.device != dev:
+            raise _lib.FmoeError(f"module is {w.dtype} on {w.device}, input is {dtype} on {dev}")
+        T = x.shape[0]
+        H, I, N, nk, k = self.hidden_size, self.intermediate_size, self.num_experts, self.num_keys, self.top_k
+        bn = self.router_norm
+        training = bool(self.training) or bn.running_mean is None
+        momentum = 0.1 if bn.momentum is None else float(bn.momentum)
+
+        y = torch.empty((T, H), device=dev, dtype=dtype)
+        logits = torch.empty((T, 2 * nk), device=dev, dtype=dtype)
+        idx = torch.empty((T, k), device=dev, dtype=torch.int64) if return_routing else None
+        gates = torch.empty((T, k), device=dev, dtype=dtype) if return_routing else None
+        L = _lib.lib()
+        code = _lib.dtype_code(x)
+        ws_bytes = L.fmoe_layer_workspace_bytes(T, H, I, N, nk, k, code)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+
+        with torch.cuda.device(dev):
+            main = torch.cuda.current_stream(dev)
+            aux = self._aux_stream(dev) if self.overlap_shared_mlp else None
+            a = _lib.LayerArgs()
+            a.x = x.data_ptr()
+            a.gate_proj = self.gate_proj.weight.data_ptr()
+            a.up_proj = self.up_proj.weight.data_ptr()
+            a.down_proj = self.down_proj.weight.data_ptr()
+            a.router_gate = self.router_gate.weight.data_ptr()
+            a.down_embed = self.down_embed.weight.data_ptr()
+            a.up_embed = self.up_embed.weight.data_ptr()
+            a.running_mean = _lib.ptr(bn.running_mean)
+            a.running_var = _lib.ptr(bn.running_var)
+            a.y = y.data_ptr()
+            a.router_logits = logits.data_ptr()
+            a.indices_out = _lib.ptr(idx)
+            a.gates_out = _lib.ptr(gates)
+            a.workspace = ws.data_ptr()
+            a.workspace_bytes = ws_bytes
+            a.status = _lib.status_word(dev).data_ptr()
+            a.stream = main.cuda_stream
+            a.aux_stream = aux.cuda_stream if aux is not None else None
+            a.stage_events = stage_timer.c_array() if stage_timer is not None else None
+            a.num_tokens, a.num_experts = T, N
+            a.hidden, a.intermediate, a.num_keys, a.top_k = H, I, nk, k
+            a.dtype = code
+            a.training = int(training)
+            a.norm_topk_prob = int(bool(self.norm_topk_prob))
+            a.bn_momentum = momentum
+            a.bn_eps = float(bn.eps)
+            rc = L.fmoe_layer_forward(ctypes.byref(a))
+        _lib.check(rc, "fmoe_layer_forward")
+        if aux is not None:
+            # the workspace and the inputs were also used on the side stream
+            ws.record_stream(aux)
+            x.record_stream(aux)
+        if training and bn.num_batches_tracked is not None and self.training:
+            bn.num_batches_tracked += 1
+        if return_routing:
+            self.last_indices, self.last_gates = idx, gates
+        router_logits = logits.view(T, 2, nk).transpose(0, 1)
+        return y.view(bsz, seq_len, H), router_logits

@@ -1,0 +1,58 @@
+"""Fine-grained expert forward (drop-in for flash_moe/ops/triton/flash_expert.py:831-836)."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from .utils import ForwardOnly, contiguous
+
+
+def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, out_dtype=None):
+    dev = _lib.require_cuda(hidden_states, down_weights, up_weights, indices, routing_weights)
+    x, d, u, idx, g = (contiguous(t) for t in (hidden_states, down_weights, up_weights, indices, routing_weights))
+    if x.dim() != 2 or d.dim() != 2 or u.dim() != 2 or idx.dim() != 2:
+        raise _lib.FmoeError("expected hidden_states[T,H], down/up_weights[N,H], indices[T,k]")
+    T, H = x.shape
+    N = d.shape[0]
+    k = idx.shape[1]
+    if d.shape != u.shape or d.shape[1] != H or idx.shape[0] != T or tuple(g.shape) != (T, k):
+        raise _lib.FmoeError("shape mismatch between hidden_states, expert tables, indices and routing_weights")
+    if not (d.dtype == u.dtype == x.dtype):
+        raise _lib.FmoeError("hidden_states and the expert tables must share one dtype")
+    if idx.dtype != torch.int64:
+        idx = idx.to(torch.int64)
+    if g.dtype != x.dtype:
+        g = g.to(x.dtype)
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    out = torch.empty((T, H), device=dev, dtype=out_dtype)
+    L = _lib.lib()
+    ws_bytes = L.fmoe_expert_workspace_bytes(T, H, N, k)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.fmoe_expert_forward(
+            x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), out.data_ptr(),
+            _lib.dtype_code(x), _lib.DTYPE_CODE[out_dtype], T, H, N, k, ws.data_ptr(), ws_bytes,
+            _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+        )
+    _lib.check(rc, "fmoe_expert_forward")
+    return out
+
+
+class FlashExpertFunc(ForwardOnly):
+    @staticmethod
+    def forward(ctx, hidden_states, down_weights, up_weights, indices, routing_weights):
+        return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights)
+
+
+def flash_expert_func(hidden_states, down_weights, up_weights, indices, routing_weights):
+    """experts_states[T,H] = sum_j silu(<x, down[idx_j]>) * routing_weights_j * up[idx_j], in hidden_states.dtype."""
+    return FlashExpertFunc.apply(hidden_states, down_weights, up_weights, indices, routing_weights)
+
+
+def flash_expert_fp32(hidden_states, down_weights, up_weights, indices, routing_weights):
+    """Same sum returned as the unrounded float32 accumulator."""
+    return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, torch.float32)
+
+
+triton_flash_expert_func = flash_expert_func

@@ -1,0 +1,56 @@
+"""Shared SwiGLU MLP (drop-in for flash_moe/ops/triton/flash_mlp.py:169-181)."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from .utils import ForwardOnly, contiguous
+
+
+def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None):
+    dev = _lib.require_cuda(x, gate_weight, up_weight, down_weight, addend)
+    lead = x.shape[:-1]
+    H = x.shape[-1]
+    x2, wg, wu, wd = (contiguous(t) for t in (x.reshape(-1, H), gate_weight, up_weight, down_weight))
+    T = x2.shape[0]
+    I = wg.shape[0]
+    if wg.shape != (I, H) or wu.shape != (I, H) or wd.shape != (H, I):
+        raise _lib.FmoeError("expected gate/up_weight[I,H] and down_weight[H,I]")
+    if not (wg.dtype == wu.dtype == wd.dtype == x2.dtype):
+        raise _lib.FmoeError("x and the MLP weights must share one dtype")
+    if addend is not None:
+        addend = contiguous(addend.reshape(-1, H))
+        if addend.dtype != torch.float32 or addend.shape != (T, H):
+            raise _lib.FmoeError("addend must be float32 [T,H]")
+    out = torch.empty((T, H), device=dev, dtype=x2.dtype)
+    L = _lib.lib()
+    code = _lib.dtype_code(x2)
+    ws_bytes = L.fmoe_mlp_workspace_bytes(T, H, I, code)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.fmoe_mlp_forward(
+            x2.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), _lib.ptr(addend), out.data_ptr(), code, T, H, I,
+            ws.data_ptr(), ws_bytes, _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+        )
+    _lib.check(rc, "fmoe_mlp_forward")
+    return out.view(*lead, H)
+
+
+class FlashMLPFunc(ForwardOnly):
+    @staticmethod
+    def forward(ctx, x, gate_weight, up_weight, down_weight):
+        return _mlp_forward(x, gate_weight, up_weight, down_weight)
+
+
+def flash_mlp_func(x, gate_weight, up_weight, down_weight):
+    """(silu(x Wg^T) * (x Wu^T)) Wd^T with the activation fused into the first GEMM's epilogue."""
+    return FlashMLPFunc.apply(x, gate_weight, up_weight, down_weight)
+
+
+def flash_mlp_add(x, gate_weight, up_weight, down_weight, addend_fp32):
+    """Same with a float32 [T,H] addend summed into the accumulator before the single rounding."""
+    return _mlp_forward(x, gate_weight, up_weight, down_weight, addend_fp32)
+
+
+triton_flash_mlp_func = flash_mlp_func

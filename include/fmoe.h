@@ -1,0 +1,168 @@
+/*
+ * fmoe.h - C ABI of libfmoe_sm100a.so: the forward hot path of the FlashMoE layer
+ * (product-key router -> fine-grained experts -> shared SwiGLU MLP) as hand-written
+ * CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - every data pointer is a DEVICE pointer, row-major and contiguous unless stated;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and the
+ *     functions return without synchronising the host;
+ *   - nothing is allocated inside: scratch memory comes from the caller through
+ *     (`workspace`, `workspace_bytes`), sized by the matching *_workspace_bytes query;
+ *   - return value: 0 = ok, > 0 = argument error found on the host (FMOE_ERR_*),
+ *     < 0 = a CUDA runtime/driver error code, negated;
+ *   - `status` (nullable) points to one int32 in device memory that kernels OR flags
+ *     into (FMOE_STATUS_*): out-of-range expert ids are skipped and reported there, a
+ *     device-side wait that ran out is reported there; the caller zeroes and reads it.
+ *
+ * Reference interfaces replaced (paths inside the flash-algo/flash-moe project) are
+ * cited on each entry point.
+ */
+#ifndef FMOE_H_
+#define FMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fmoe_stream_t; /* cudaStream_t */
+
+enum fmoe_dtype { FMOE_DTYPE_F32 = 0, FMOE_DTYPE_BF16 = 1, FMOE_DTYPE_F16 = 2 };
+
+enum fmoe_error {
+  FMOE_OK = 0,
+  FMOE_ERR_BAD_ARG = 1,     /* null pointer, negative size, k > num_keys ... */
+  FMOE_ERR_UNSUPPORTED = 2, /* a shape/dtype combination no kernel covers */
+  FMOE_ERR_WORKSPACE = 3,   /* workspace missing or too small */
+  FMOE_ERR_ALIGNMENT = 4    /* pointer or row pitch not 16-byte aligned */
+};
+
+enum fmoe_status_bits {
+  FMOE_STATUS_BAD_EXPERT_ID = 1, /* an index outside [0, num_experts) was skipped */
+  FMOE_STATUS_WAIT_TIMEOUT = 2   /* a bounded device-side wait gave up */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fmoe_version(void);
+/* Static string for a return code of this library. */
+const char* fmoe_error_string(int code);
+
+/*
+ * Product-key router top-k.
+ * Replaces triton_flash_router_func(router_logits, num_expert_keys, num_experts_per_tok)
+ *   flash_moe/ops/triton/flash_router.py:381-382 (forward: :252-314, kernels :8-194).
+ * log_probs [2, T, num_keys] of `dtype`; scores [T, top_k] of `dtype`; indices [T, top_k] int64.
+ * Result = the top_k candidates (i, j) of log_probs[0,t,i] + log_probs[1,t,j] (sum formed in
+ * `dtype`), flat id i*num_keys + j, in descending score order, equal scores ordered by
+ * ascending flat id - the order the reference's repeated arg-max produces.
+ * gates (nullable) [T, top_k] of `dtype`: exp(score) rounded to `dtype`, divided by its row
+ * sum when norm_topk_prob != 0 (flash_moe/modules/flash_moe.py:80-85).
+ * Requires 0 <= top_k <= num_keys (flash_router.py:261).
+ */
+int fmoe_router_topk(const void* log_probs, int dtype, int64_t num_tokens, int num_keys, int top_k, void* scores,
+                     int64_t* indices, void* gates, int norm_topk_prob, fmoe_stream_t stream);
+
+/*
+ * Router front end: BatchNorm1d(affine=False) -> Linear(H, 2*num_keys, bias=False) -> per-half log-softmax.
+ * Replaces flash_moe/modules/flash_moe.py:65-72 (router_norm :49, router_gate :48).
+ * x [T, H]; router_weight [2*num_keys, H]; running_mean / running_var [H] in `dtype` (the module
+ * casts its buffers with its parameters); training != 0 uses batch statistics (biased variance)
+ * and updates the running buffers in place with `momentum` (unbiased variance), as torch does.
+ * logits [T, 2*num_keys] (half h = columns h*num_keys ..), log_probs [2, T, num_keys], both `dtype`.
+ */
+size_t fmoe_router_front_workspace_bytes(int64_t num_tokens, int hidden, int num_keys, int dtype);
+int fmoe_router_front(const void* x, const void* router_weight, void* running_mean, void* running_var, int training,
+                      float momentum, float eps, void* logits, void* log_probs, int dtype, int64_t num_tokens,
+                      int hidden, int num_keys, void* workspace, size_t workspace_bytes, int32_t* status,
+                      fmoe_stream_t stream);
+
+/*
+ * Fine-grained experts: out[t] = sum_j silu(<x[t], down[idx[t,j]]>) * gates[t,j] * up[idx[t,j]].
+ * Replaces triton_flash_expert_func(hidden_states, down_weights, up_weights, indices, routing_weights)
+ *   flash_moe/ops/triton/flash_expert.py:831-836 (forward :580-649, preprocessing :528-577,
+ *   kernels :13-211).
+ * x [T, H], down/up [N, H], gates [T, k] of `dtype`; indices [T, k] int64 (duplicates inside a
+ * token accumulate; ids outside [0, N) are skipped and flagged in *status).
+ * out [T, H] of `out_dtype`: `dtype` (one rounding of the fp32 sum) or FMOE_DTYPE_F32.
+ */
+size_t fmoe_expert_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k);
+int fmoe_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
+                        void* out, int dtype, int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts,
+                        int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+
+/*
+ * Shared SwiGLU MLP: out = (silu(x Wg^T) * (x Wu^T)) Wd^T  (+ addend).
+ * Replaces triton_flash_mlp_func(x, gate_weight, up_weight, down_weight)
+ *   flash_moe/ops/triton/flash_mlp.py:169-181 and the final add flash_moe/modules/flash_moe.py:101.
+ * x [T, H], gate_w / up_w [I, H], down_w [H, I], out [T, H] of `dtype`;
+ * addend (nullable) [T, H] float32 is added to the fp32 accumulator before the single rounding.
+ */
+size_t fmoe_mlp_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int dtype);
+int fmoe_mlp_forward(const void* x, const void* gate_w, const void* up_w, const void* down_w, const float* addend,
+                     void* out, int dtype, int64_t num_tokens, int hidden, int intermediate, void* workspace,
+                     size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+
+/*
+ * Whole layer forward.  Replaces FlashMoE.forward, flash_moe/modules/flash_moe.py:55-105.
+ * Parameter names follow the module: gate_proj/up_proj [I,H], down_proj [H,I], router_gate
+ * [2*num_keys, H], down_embed/up_embed [N, H], router_norm running buffers [H].
+ * Outputs: y [T, H]; router_logits [T, 2*num_keys] (the module returns it viewed as
+ * (2, T, num_keys)); optional indices [T,k] int64 and gates [T,k] for inspection.
+ * aux_stream (nullable): a second stream the shared MLP may run on concurrently with routing.
+ * stage_events (nullable): host array of 2*FMOE_NUM_STAGES cudaEvent_t handles; entry 2*s is
+ * recorded before and 2*s+1 after stage s (enum fmoe_stage) on the stream that stage runs on,
+ * so a caller can time the stages of a real forward with cudaEventElapsedTime.
+ */
+enum fmoe_stage {
+  FMOE_STAGE_ROUTER_FRONT = 0, /* batch-norm + sub-key GEMM + log-softmax */
+  FMOE_STAGE_ROUTER_TOPK = 1,
+  FMOE_STAGE_EXPERTS = 2,
+  FMOE_STAGE_MLP_UP = 3,   /* h = silu(x Wg^T) * (x Wu^T) */
+  FMOE_STAGE_MLP_DOWN = 4, /* y = h Wd^T + experts */
+  FMOE_NUM_STAGES = 5
+};
+
+typedef struct fmoe_layer_args {
+  const void* x;
+  const void* gate_proj;
+  const void* up_proj;
+  const void* down_proj;
+  const void* router_gate;
+  const void* down_embed;
+  const void* up_embed;
+  void* running_mean;
+  void* running_var;
+  void* y;
+  void* router_logits;
+  int64_t* indices_out; /* nullable */
+  void* gates_out;      /* nullable */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status; /* nullable */
+  fmoe_stream_t stream;
+  fmoe_stream_t aux_stream; /* nullable */
+  void* const* stage_events; /* nullable */
+  int64_t num_tokens;
+  int64_t num_experts;
+  int32_t hidden;
+  int32_t intermediate;
+  int32_t num_keys;
+  int32_t top_k;
+  int32_t dtype;
+  int32_t training;
+  int32_t norm_topk_prob;
+  float bn_momentum;
+  float bn_eps;
+} fmoe_layer_args;
+
+size_t fmoe_layer_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int64_t num_experts, int num_keys,
+                                  int top_k, int dtype);
+int fmoe_layer_forward(const fmoe_layer_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMOE_H_ */

@@ -1,0 +1,132 @@
+"""Expert and shared-MLP parity on the GPU through the C ABI (fmoe_expert_forward / fmoe_mlp_forward)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import flashmoe_oracle as O
+from tests.helpers import randn
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2  # max |err| / RMS(oracle), the layer-output budget for 16-bit results
+F32_TOL = 2e-5
+
+
+def expert_inputs(T, H, N, k, dtype, seed=0, zipf=False):
+    x = randn((T, H), seed + 1, dtype, 0.5)
+    d = randn((N, H), seed + 2, dtype, 0.1)
+    u = randn((N, H), seed + 3, dtype, 0.1)
+    g = torch.Generator().manual_seed(seed + 4)
+    if zipf:
+        p = torch.arange(1, N + 1, dtype=torch.float64).pow(-1.1)
+        cdf = torch.cumsum(p / p.sum(), 0)
+        idx = torch.searchsorted(cdf, torch.rand(T, k, generator=g, dtype=torch.float64)).clamp_(max=N - 1)
+    else:
+        idx = torch.randint(0, N, (T, k), generator=g)
+    gates = torch.softmax(torch.randn(T, k, generator=g), dim=-1).to(dtype)
+    return x, d, u, idx, gates
+
+
+@pytest.mark.parametrize(
+    "T,H,N,k",
+    [(64, 256, 1024, 8), (300, 1024, 4096, 16), (17, 72, 50, 3), (128, 2048, 512, 4), (33, 4096, 64, 2),
+     (256, 512, 7, 5), (1, 128, 16, 1)],
+)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_expert_forward(T, H, N, k, dtype):
+    from flash_moe_b200 import check_status
+    from flash_moe_b200.ops.flash_expert import flash_expert_fp32, flash_expert_func
+
+    if dtype == torch.float32 and H % 4:
+        pytest.skip("row size must be a multiple of 16 bytes")
+    x, d, u, idx, gates = expert_inputs(T, H, N, k, dtype, seed=T + H)
+    idx[0, -1] = idx[0, 0]  # duplicate expert inside a token accumulates
+    want = O.expert_forward(x, d, u, idx, gates)
+    got = flash_expert_func(x.cuda(), d.cuda(), u.cuda(), idx.cuda(), gates.cuda())
+    acc = flash_expert_fp32(x.cuda(), d.cuda(), u.cuda(), idx.cuda(), gates.cuda())
+    again = flash_expert_func(x.cuda(), d.cuda(), u.cuda(), idx.cuda(), gates.cuda())
+    check_status()
+    assert got.dtype == dtype and acc.dtype == torch.float32
+    assert O.rel_rms_error(acc.cpu(), want) < F32_TOL * 10
+    assert O.rel_rms_error(got.cpu().float(), want) < (F32_TOL * 10 if dtype == torch.float32 else BF16_TOL)
+    assert torch.equal(got, again), "the expert path must be run-to-run deterministic"
+
+
+def test_expert_zipf_hot_expert_and_empty_experts():
+    from flash_moe_b200.ops.flash_expert import flash_expert_fp32
+
+    T, H, N, k = 512, 256, 65536, 16
+    x, d, u, idx, gates = expert_inputs(T, H, N, k, torch.bfloat16, seed=9, zipf=True)
+    assert torch.bincount(idx.flatten(), minlength=N).max() > 200  # one expert owns many pairs
+    want = O.expert_forward(x, d, u, idx, gates)
+    got = flash_expert_fp32(x.cuda(), d.cuda(), u.cuda(), idx.cuda(), gates.cuda())
+    assert O.rel_rms_error(got.cpu(), want) < 1e-4
+    idx[:] = 3  # every pair on one expert
+    want = O.expert_forward(x, d, u, idx, gates)
+    got = flash_expert_fp32(x.cuda(), d.cuda(), u.cuda(), idx.cuda(), gates.cuda())
+    assert O.rel_rms_error(got.cpu(), want) < 1e-4
+
+
+def test_expert_out_of_range_ids_are_skipped_and_flagged():
+    from flash_moe_b200 import read_status
+    from flash_moe_b200.ops.flash_expert import flash_expert_fp32
+
+    T, H, N, k = 32, 128, 64, 4
+    x, d, u, idx, gates = expert_inputs(T, H, N, k, torch.bfloat16, seed=2)
+    read_status()
+    bad = idx.clone()
+    bad[3, 1] = N
+    bad[5, 0] = -1
+    got = flash_expert_fp32(x.cuda(), d.cuda(), u.cuda(), bad.cuda(), gates.cuda())
+    assert read_status() & 1
+    g2 = gates.clone()
+    g2[3, 1] = 0
+    g2[5, 0] = 0
+    want = O.expert_forward(x, d, u, bad.clamp(0, N - 1), g2)
+    assert O.rel_rms_error(got.cpu(), want) < 1e-4
+    assert read_status() == 0
+
+
+def test_expert_matches_reference_kernel_fixture(golden_dir):
+    from flash_moe_b200.ops.flash_expert import flash_expert_func
+
+    z = np.load(os.path.join(golden_dir, "triton_expert_small.npz"))
+    t = {n: torch.from_numpy(z[n]).cuda() for n in z.files}
+    got = flash_expert_func(t["x"], t["down"], t["up"], t["indices"], t["gates"])
+    np.testing.assert_allclose(got.cpu().numpy(), z["y"], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize(
+    "T,H,I", [(256, 256, 1024), (200, 136, 264), (128, 1024, 4096), (1000, 512, 384), (3, 64, 128), (129, 128, 8)]
+)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_mlp_forward(T, H, I, dtype):
+    from flash_moe_b200 import check_status
+    from flash_moe_b200.ops.flash_mlp import flash_mlp_add, flash_mlp_func
+
+    x = randn((T, H), 1, dtype, 0.5)
+    wg = randn((I, H), 2, dtype, 1.0 / H**0.5)
+    wu = randn((I, H), 3, dtype, 1.0 / H**0.5)
+    wd = randn((H, I), 4, dtype, 1.0 / I**0.5)
+    add = randn((T, H), 5, torch.float32, 0.3)
+    want = O.mlp_forward(x, wg, wu, wd)
+    got = flash_mlp_func(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    got_add = flash_mlp_add(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), add.cuda())
+    again = flash_mlp_func(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    check_status()
+    tol = 1e-4 if dtype == torch.float32 else BF16_TOL
+    assert O.rel_rms_error(got.cpu().float(), want) < tol
+    assert O.rel_rms_error(got_add.cpu().float(), want + add) < tol
+    assert torch.equal(got, again)
+
+
+def test_mlp_matches_reference_kernel_fixture(golden_dir):
+    from flash_moe_b200.ops.flash_mlp import flash_mlp_func
+
+    z = np.load(os.path.join(golden_dir, "triton_mlp_small.npz"))
+    t = {n: torch.from_numpy(z[n]).cuda() for n in z.files}
+    got = flash_mlp_func(t["x"], t["wg"], t["wu"], t["wd"])
+    np.testing.assert_allclose(got.cpu().numpy(), z["y"], rtol=1e-4, atol=1e-5)

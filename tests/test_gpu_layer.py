@@ -1,0 +1,129 @@
+"""Whole-layer parity on the GPU (fmoe_layer_forward behind the FlashMoE module)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import flashmoe_oracle as O
+from tests.helpers import bf16_ulp_close, make_layer_pair, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def run_layer(ours, x, **kw):
+    from flash_moe_b200 import check_status
+
+    with torch.no_grad():
+        y, logits = ours(x.cuda(), return_routing=True, **kw)
+    torch.cuda.synchronize()
+    check_status()
+    return y.cpu(), logits.cpu(), ours.last_indices.cpu(), ours.last_gates.cpu()
+
+
+def chained_checks(ref, x, y, logits, idx, gates, dtype, out_tol):
+    """The parity chain: our logits vs fp32, the reference routing applied to OUR logits, and the
+    outputs vs an fp32 evaluation teacher-forced on our indices and gates."""
+    T = x.shape[0] * x.shape[1]
+    nk, k = ref.num_keys, ref.top_k
+    x2 = x.reshape(T, -1)
+    with torch.no_grad():
+        bn = ref.router_norm
+        want_logits, _ = O.router_front(
+            x2.float(), ref.router_gate.weight.float(),
+            bn.running_mean.float().clone(), bn.running_var.float().clone(), False,
+        )
+        lg = logits.transpose(0, 1).reshape(T, 2 * nk)
+        assert O.rel_rms_error(lg.float(), want_logits) < (2e-2 if dtype != torch.float32 else 1e-4)
+        # reference routing on our logits
+        lp = torch.log_softmax(logits.float(), dim=-1).to(dtype).contiguous()
+        want_s, want_i = O.router_topk(lp, nk, k)
+        viol = O.check_router_threshold(lp, nk, k, idx, rel=1e-3 if dtype == torch.float32 else 8e-3)
+        assert all(v == 0 for v in viol.values()), viol
+        same = (torch.sort(idx, -1).values == torch.sort(want_i, -1).values).all(-1).float().mean().item()
+        assert same > (0.999 if dtype == torch.float32 else 0.97), same
+        want_g = O.routing_weights(want_s, ref.norm_topk_prob)
+        rows = (idx == want_i).all(-1)
+        if dtype == torch.float32:
+            torch.testing.assert_close(gates[rows], want_g[rows], rtol=1e-4, atol=1e-7)
+        else:
+            assert bf16_ulp_close(gates[rows], want_g[rows], 2).all()
+        want_y = ref.forward_fp32_given_routing(x, idx, gates)
+    err = O.rel_rms_error(y.float(), want_y)
+    assert err < out_tol, err
+    return err
+
+
+def test_layer_config1_fp32_matches_reference_fixture(golden_dir):
+    """BASELINE config 1 (T=256, H=256, I=1024, N=1024, k=8, fp32): against the output the
+    reference's eager module produced for the same seeds."""
+    z = np.load(os.path.join(golden_dir, "eager_c1_fp32.npz"))
+    ref, ours = make_layer_pair(256, 1024, 1024, 8, False, torch.float32)
+    ref.eval(); ours.eval()
+    x = torch.randn(1, 256, 256, generator=torch.Generator().manual_seed(1))
+    y, logits, idx, gates = run_layer(ours, x)
+    np.testing.assert_allclose(logits.contiguous().numpy(), z["router_logits"], rtol=1e-4, atol=2e-5)
+    same = (np.sort(idx.numpy(), -1) == np.sort(z["indices"], -1)).all(-1).mean()
+    assert same > 0.99
+    rms = float(np.sqrt((z["y"] ** 2).mean()))
+    rows = (np.sort(idx.numpy(), -1) == np.sort(z["indices"], -1)).all(-1)
+    assert np.abs(y.numpy()[0][rows] - z["y"][0][rows]).max() < 1e-3 * rms
+    chained_checks(ref, x, y, logits, idx, gates, torch.float32, 1e-4)
+
+
+@pytest.mark.parametrize(
+    "H,I,N,k,norm,B,S",
+    [(256, 1024, 1024, 8, False, 1, 256), (512, 768, 4096, 16, True, 2, 192), (128, 256, 256, 4, False, 3, 50),
+     (1024, 4096, 16384, 64, False, 1, 512)],
+)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_layer_16bit_chained_parity(H, I, N, k, norm, B, S, dtype):
+    ref, ours = make_layer_pair(H, I, N, k, norm, dtype)
+    ref.eval(); ours.eval()
+    x = randn((B, S, H), 1, dtype)
+    y, logits, idx, gates = run_layer(ours, x)
+    chained_checks(ref, x, y, logits, idx, gates, dtype, 2e-2)
+    y2, *_ = run_layer(ours, x)
+    assert torch.equal(y, y2)
+
+
+def test_layer_train_mode_batch_statistics():
+    ref, ours = make_layer_pair(256, 512, 1024, 8, True, torch.float32)
+    ref.train(); ours.train()
+    x = randn((2, 128, 256), 3) * 1.5 + 0.3
+    with torch.no_grad():
+        want_y, want_logits = ref(x)
+    y, logits, idx, gates = run_layer(ours, x)
+    torch.testing.assert_close(logits.contiguous(), want_logits.contiguous(), rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(ours.router_norm.running_mean.cpu(), ref.router_norm.running_mean, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(ours.router_norm.running_var.cpu(), ref.router_norm.running_var, rtol=1e-4, atol=1e-6)
+    assert int(ours.router_norm.num_batches_tracked) == 1
+
+
+def test_layer_config2_full_size_bf16():
+    """BASELINE config 2 (T=4096, H=1024, I=4096, N=16384, k=64, bf16), teacher-forced output parity and
+    the same result with the shared MLP on the main stream."""
+    ref, ours = make_layer_pair(1024, 4096, 16384, 64, False, torch.bfloat16)
+    ref.eval(); ours.eval()
+    x = randn((1, 4096, 1024), 1, torch.bfloat16)
+    y, logits, idx, gates = run_layer(ours, x)
+    err = chained_checks(ref, x, y, logits, idx, gates, torch.bfloat16, 2e-2)
+    print("config 2 teacher-forced error / RMS:", err)
+    ours.overlap_shared_mlp = False
+    y2, *_ = run_layer(ours, x)
+    assert torch.equal(y, y2)
+
+
+def test_state_dict_and_forward_only_contract():
+    from flash_moe_b200 import FlashMoE, FlashMoEConfig
+
+    ref, ours = make_layer_pair(128, 256, 256, 4, False, torch.bfloat16)
+    assert set(ref.state_dict()) == set(ours.state_dict())
+    other = FlashMoE(FlashMoEConfig(128, 256, "silu", 256, 4)).to(torch.bfloat16).cuda()
+    other.load_state_dict(ref.state_dict())
+    x = randn((1, 64, 128), 2, torch.bfloat16).cuda()
+    ours.eval(); other.eval()
+    assert torch.equal(ours(x)[0], other(x)[0])
+    with pytest.raises(Exception):
+        ours(x.cpu())
