@@ -214,13 +214,116 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
   }
 }
 
+// ---------------------------------------------------------------- 2b. scores per token on mma.sync
+// Token-centric scores for 16-bit dtypes when the tables are small enough to stay in L2: no
+// sort.  One warp per token; groups of 16 of its experts form the A operand (their down rows,
+// gathered with 128-bit loads), the token's x row is every column of B, so each accumulator
+// column holds <x, D[e]> for the 16 rows (fp32 accumulate).  The k index inside a 32-column
+// block is permuted identically for A and B so that every thread's 16-byte load feeds two MMAs.
+template <typename T> struct Mma16816;
+template <> struct Mma16816<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <> struct Mma16816<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restrict__ x, const T* __restrict__ down,
+                                                               const int64_t* __restrict__ idx,
+                                                               const T* __restrict__ gates, float* __restrict__ gs,
+                                                               int64_t ntok, int H, int64_t N, int k,
+                                                               int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  bool bad = false;
+  for (int64_t t = warp_global; t < ntok; t += warps_total) {
+    const T* xr = x + t * H;
+    for (int j0 = 0; j0 < k; j0 += 64) {
+      const int ngroups = min(4, (k - j0 + 15) >> 4);
+      const T* ra[4];
+      const T* rb[4];
+      bool oka[4], okb[4];
+#pragma unroll
+      for (int G = 0; G < 4; ++G) {
+        const int ja = j0 + G * 16 + g, jb = ja + 8;
+        int64_t ea = 0, eb = 0;
+        if (ja < k) ea = idx[t * k + ja];
+        if (jb < k) eb = idx[t * k + jb];
+        oka[G] = (ja < k) && ea >= 0 && ea < N;
+        okb[G] = (jb < k) && eb >= 0 && eb < N;
+        if ((ja < k && !oka[G]) || (jb < k && !okb[G])) bad = true;
+        ra[G] = down + (oka[G] ? ea : 0) * H;
+        rb[G] = down + (okb[G] ? eb : 0) * H;
+      }
+      float c[4][4];
+#pragma unroll
+      for (int G = 0; G < 4; ++G)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[G][i] = 0.f;
+#pragma unroll 2
+      for (int c0 = 0; c0 < H; c0 += 32) {
+        const int col = c0 + 8 * tq;
+        const bool in = col < H;
+        const uint4 xq = in ? ldg16(xr + col) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int G = 0; G < 4; ++G) {
+          if (G < ngroups) {
+            const uint4 qa = in ? ldg16(ra[G] + col) : make_uint4(0, 0, 0, 0);
+            const uint4 qb = in ? ldg16(rb[G] + col) : make_uint4(0, 0, 0, 0);
+            Mma16816<T>::run(c[G], qa.x, qb.x, qa.y, qb.y, xq.x, xq.y);
+            Mma16816<T>::run(c[G], qa.z, qb.z, qa.w, qb.w, xq.z, xq.w);
+          }
+        }
+      }
+      if (tq == 0) {
+#pragma unroll
+        for (int G = 0; G < 4; ++G) {
+          const int ja = j0 + G * 16 + g, jb = ja + 8;
+          if (ja < k) gs[t * k + ja] = oka[G] ? silu_f32(c[G][0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
+          if (jb < k) gs[t * k + jb] = okb[G] ? silu_f32(c[G][2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
+        }
+      }
+    }
+  }
+  if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_EXPERT_ID);
+}
+
 // ---------------------------------------------------------------- 3. per-token accumulate
-// One warp per (token, column block of 32*VEC*NCH elements).
+// One warp per (token, column block of 32*VEC*NCH elements); four gathered rows in flight per
+// lane, packed f32x2 FMAs (two accumulators per instruction).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t a, uint64_t b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
 template <typename T, typename OutT, int NCH>
 __global__ void __launch_bounds__(256) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
                                                           const float* __restrict__ gs, OutT* __restrict__ out,
                                                           int64_t ntok, int H, int64_t N, int k, int colblocks) {
   constexpr int VEC = Vec16<T>::N;
+  constexpr int SLOTS = 4;
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -229,76 +332,66 @@ __global__ void __launch_bounds__(256) expert_accum_kernel(const T* __restrict__
     const int64_t t = task / colblocks;
     const int cb = static_cast<int>(task - t * colblocks);
     const int col0 = cb * (32 * VEC * NCH);
-    float acc[NCH][VEC];
+    bool in[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) in[c] = col0 + (c * 32 + lane) * VEC < H;
+    uint64_t acc[NCH][VEC / 2];
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[c][i] = 0.f;
+      for (int i = 0; i < VEC / 2; ++i) acc[c][i] = 0ull;
 
     for (int j0 = 0; j0 < k; j0 += 32) {
-      // each lane fetches one slot's (expert id, weight); invalid ids get weight 0
+      // each lane fetches one slot's (expert id, weight); invalid or absent slots get weight 0
       const int j = j0 + lane;
-      int64_t e_l = 0;
+      int e_l = 0;
       float w_l = 0.f;
       if (j < k) {
-        e_l = idx[t * k + j];
-        w_l = gs[t * k + j];
-        if (e_l < 0 || e_l >= N) { e_l = 0; w_l = 0.f; }
+        const int64_t e = idx[t * k + j];
+        if (e >= 0 && e < N) {
+          e_l = static_cast<int>(e);
+          w_l = gs[t * k + j];
+        }
       }
       const int nslots = min(32, k - j0);
-      int s = 0;
-      for (; s + 2 <= nslots; s += 2) {  // two gathered rows in flight
-        const int64_t e0 = __shfl_sync(kFull, e_l, s), e1 = __shfl_sync(kFull, e_l, s + 1);
-        const float w0 = __shfl_sync(kFull, w_l, s), w1 = __shfl_sync(kFull, w_l, s + 1);
-        const T* u0 = up + e0 * H + col0;
-        const T* u1 = up + e1 * H + col0;
-        uint4 q0[NCH], q1[NCH];
+      for (int s = 0; s < nslots; s += SLOTS) {
+        uint4 q[SLOTS][NCH];
+        uint64_t ww[SLOTS];
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          const int col = (c * 32 + lane) * VEC;
-          const bool in = col0 + col < H;
-          q0[c] = in ? ldg16(u0 + col) : make_uint4(0, 0, 0, 0);
-          q1[c] = in ? ldg16(u1 + col) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < SLOTS; ++u) {
+          const int e = __shfl_sync(kFull, e_l, s + u);
+          const float w = __shfl_sync(kFull, w_l, s + u);
+          ww[u] = pack_f32x2(w, w);
+          const T* row = up + static_cast<int64_t>(e) * H + col0 + lane * VEC;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) q[u][c] = in[c] ? ldg16(row + c * 32 * VEC) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          float f0[VEC], f1[VEC];
-          unpack16<T>(q0[c], f0);
-          unpack16<T>(q1[c], f1);
+        for (int u = 0; u < SLOTS; ++u)
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w0, f0[i], acc[c][i]);
+          for (int c = 0; c < NCH; ++c) {
+            float f[VEC];
+            unpack16<T>(q[u][c], f);
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w1, f1[i], acc[c][i]);
-        }
-      }
-      for (; s < nslots; ++s) {
-        const int64_t e0 = __shfl_sync(kFull, e_l, s);
-        const float w0 = __shfl_sync(kFull, w_l, s);
-        const T* u0 = up + e0 * H + col0;
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          const int col = (c * 32 + lane) * VEC;
-          if (col0 + col < H) {
-            float f0[VEC];
-            unpack16<T>(ldg16(u0 + col), f0);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[c][i] = fmaf(w0, f0[i], acc[c][i]);
+            for (int i = 0; i < VEC / 2; ++i) ffma2(acc[c][i], pack_f32x2(f[2 * i], f[2 * i + 1]), ww[u]);
           }
-        }
       }
     }
     OutT* orow = out + t * H + col0;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int col = (c * 32 + lane) * VEC;
-      if (col0 + col < H) {
+      if (in[c]) {
+        float f[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) unpack_f32x2(acc[c][i], f[2 * i], f[2 * i + 1]);
         if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
           for (int i = 0; i < VEC; i += 4)
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + col + i) =
-                make_float4(acc[c][i], acc[c][i + 1], acc[c][i + 2], acc[c][i + 3]);
+                make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
         } else {
-          *reinterpret_cast<uint4*>(orow + col) = pack16<OutT>(acc[c]);
+          *reinterpret_cast<uint4*>(orow + col) = pack16<OutT>(f);
         }
       }
     }
@@ -370,38 +463,52 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
-  FMOE_CUDA_TRY(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(N) * 4, stream));
-  {
-    const int64_t want = (P + 255) / 256;
-    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
-    expert_hist_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.counts, w.rank, status);
-    FMOE_LAUNCH_CHECK();
-  }
-  {
-    const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
-    if (ntiles > 16) {
-      scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums);
-      FMOE_LAUNCH_CHECK();
-      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums, w.offsets);
-    } else {
-      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, nullptr, w.offsets);
-    }
-    FMOE_LAUNCH_CHECK();
-  }
-  {
-    const int64_t want = (P + 255) / 256;
-    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
-    expert_scatter_kernel<<<grid, 256, 0, stream>>>(idx, w.rank, w.offsets, P, w.sorted_pair, w.sorted_expert);
-    FMOE_LAUNCH_CHECK();
-  }
   const int per_chunk = 32 * VEC;
   const int need = (H + per_chunk - 1) / per_chunk;
-  if (need <= 1) launch_scores<T, 1>(x, down, w, N, gates, H, k, P, stream);
-  else if (need <= 2) launch_scores<T, 2>(x, down, w, N, gates, H, k, P, stream);
-  else if (need <= 4) launch_scores<T, 4>(x, down, w, N, gates, H, k, P, stream);
-  else if (need <= 8) launch_scores<T, 8>(x, down, w, N, gates, H, k, P, stream);
-  else launch_scores<T, 0>(x, down, w, N, gates, H, k, P, stream);
-  FMOE_LAUNCH_CHECK();
+  // Tables that stay resident in the 126 MB L2 are gathered per token (no sort, tensor-core dot
+  // products); larger tables take the expert-centric order so each down row leaves HBM once.
+  const bool token_centric = sizeof(T) == 2 && (2.0 * static_cast<double>(N) * H * sizeof(T) <= 96.0 * 1024 * 1024);
+  if (token_centric) {
+    if constexpr (sizeof(T) == 2) {
+      const int64_t want = (T_ + 3) / 4;
+      const int64_t cap = static_cast<int64_t>(sms) * 16;
+      const int grid = static_cast<int>(want < cap ? want : cap);
+      expert_scores_mma_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down), idx,
+                                                           static_cast<const T*>(gates), w.gs, T_, H, N, k, status);
+      FMOE_LAUNCH_CHECK();
+    }
+  } else {
+    FMOE_CUDA_TRY(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(N) * 4, stream));
+    {
+      const int64_t want = (P + 255) / 256;
+      const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+      expert_hist_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.counts, w.rank, status);
+      FMOE_LAUNCH_CHECK();
+    }
+    {
+      const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
+      if (ntiles > 16) {
+        scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums);
+        FMOE_LAUNCH_CHECK();
+        scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums, w.offsets);
+      } else {
+        scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, nullptr, w.offsets);
+      }
+      FMOE_LAUNCH_CHECK();
+    }
+    {
+      const int64_t want = (P + 255) / 256;
+      const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+      expert_scatter_kernel<<<grid, 256, 0, stream>>>(idx, w.rank, w.offsets, P, w.sorted_pair, w.sorted_expert);
+      FMOE_LAUNCH_CHECK();
+    }
+    if (need <= 1) launch_scores<T, 1>(x, down, w, N, gates, H, k, P, stream);
+    else if (need <= 2) launch_scores<T, 2>(x, down, w, N, gates, H, k, P, stream);
+    else if (need <= 4) launch_scores<T, 4>(x, down, w, N, gates, H, k, P, stream);
+    else if (need <= 8) launch_scores<T, 8>(x, down, w, N, gates, H, k, P, stream);
+    else launch_scores<T, 0>(x, down, w, N, gates, H, k, P, stream);
+    FMOE_LAUNCH_CHECK();
+  }
 
 #define FMOE_ACCUM(NCH_)                                                                       \
   do {                                                                                         \

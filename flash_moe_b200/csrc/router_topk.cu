@@ -64,7 +64,7 @@ struct RouterSmemLayout {
 };
 
 template <typename T>
-__global__ void router_topk_kernel(const T* __restrict__ logp, int64_t ntok, int nk, int k, RouterSmemLayout L,
+__global__ void router_topk_smem_kernel(const T* __restrict__ logp, int64_t ntok, int nk, int k, RouterSmemLayout L,
                                    T* __restrict__ scores, int64_t* __restrict__ indices, T* __restrict__ gates,
                                    int norm) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -232,6 +232,351 @@ __global__ void router_topk_kernel(const T* __restrict__ logp, int64_t ntok, int
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Register-resident variant for num_keys <= 1024: each half is sorted by a shuffle-based bitonic
+// network (E = padded num_keys / 32 keys per lane), sort keys are 32-bit for 16-bit dtypes
+// (16-bit order key | inverted index) and 64-bit for float32.  Shared memory only holds the
+// sorted halves (for the candidate gathers and binary searches), the index-order values, the
+// candidate scores and the winners.
+// ------------------------------------------------------------------------------------------
+template <typename T> struct HalfKey;  // sort key of one router half
+template <> struct HalfKey<float> {
+  using type = uint64_t;
+  static __device__ __forceinline__ uint64_t make(float v, uint32_t i) { return make_key(f32_to_ord(v), i); }
+  static __device__ __forceinline__ float value(uint64_t k) { return key_val(k); }
+  static __device__ __forceinline__ uint32_t id(uint64_t k) { return key_id(k); }
+};
+template <typename T16> struct HalfKey16 {
+  using type = uint32_t;
+  static __device__ __forceinline__ uint32_t make(float v, uint32_t i) {
+    const T16 h = from_f32<T16>(v);  // exact: v came from a T16
+    uint32_t b = *reinterpret_cast<const uint16_t*>(&h);
+    b ^= (b >> 15) ? 0xFFFFu : 0x8000u;
+    return (b << 16) | (0xFFFFu - i);
+  }
+  static __device__ __forceinline__ float value(uint32_t k) {
+    uint32_t b = k >> 16;
+    b ^= (b >> 15) ? 0x8000u : 0xFFFFu;
+    const uint16_t raw = static_cast<uint16_t>(b);
+    return to_f32<T16>(*reinterpret_cast<const T16*>(&raw));
+  }
+  static __device__ __forceinline__ uint32_t id(uint32_t k) { return 0xFFFFu - (k & 0xFFFFu); }
+};
+template <> struct HalfKey<__nv_bfloat16> : HalfKey16<__nv_bfloat16> {};
+template <> struct HalfKey<__half> : HalfKey16<__half> {};
+
+__device__ __forceinline__ uint32_t shfl_xor_key(uint32_t v, int m) { return __shfl_xor_sync(kFull, v, m); }
+__device__ __forceinline__ uint64_t shfl_xor_key(uint64_t v, int m) {
+  return static_cast<uint64_t>(__shfl_xor_sync(kFull, static_cast<unsigned long long>(v), m));
+}
+
+// Descending bitonic sort of 32*E keys held as element i = r*32 + lane in a[r].
+template <int E, typename K>
+__device__ __forceinline__ void bitonic_desc_regs(K (&a)[E], int lane) {
+  constexpr int n = 32 * E;
+#pragma unroll
+  for (int size = 2; size <= n; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= 32) {
+        const int rs = stride >> 5;
+#pragma unroll
+        for (int r = 0; r < E; ++r) {
+          if ((r & rs) == 0) {
+            const bool desc = (((r << 5) & size) == 0);  // size >= 64 here: decided by r alone
+            const K x = a[r], y = a[r | rs];
+            const K hi = x > y ? x : y, lo = x > y ? y : x;
+            a[r] = desc ? hi : lo;
+            a[r | rs] = desc ? lo : hi;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < E; ++r) {
+          const K other = shfl_xor_key(a[r], stride);
+          const int i = (r << 5) | lane;
+          const bool desc = ((i & size) == 0);
+          const bool lower = ((lane & stride) == 0);
+          const K hi = a[r] > other ? a[r] : other, lo = a[r] > other ? other : a[r];
+          a[r] = (lower == desc) ? hi : lo;
+        }
+      }
+    }
+  }
+}
+
+struct RouterRegLayout {
+  int cta_bytes, warp_bytes;
+  int off_sorted, off_ids, off_win, off_cs;
+  int nkp, kp, kq, C, Cp;
+};
+
+template <typename T, int E>
+__global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restrict__ logp, int64_t ntok, int nk, int k,
+                                                             RouterRegLayout L, T* __restrict__ scores,
+                                                             int64_t* __restrict__ indices, T* __restrict__ gates,
+                                                             int norm) {
+  using HK = HalfKey<T>;
+  using K = typename HK::type;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int kq = L.kq, C = L.C, nkp = L.nkp, kp = L.kp;
+
+  uint32_t* pq = reinterpret_cast<uint32_t*>(smem);
+  int* rowstart = reinterpret_cast<int*>(smem) + L.Cp;
+  if (warp == 0) {
+    int running = 0;
+    for (int base = 0; base < kq; base += 32) {
+      const int p = base + lane;
+      const int len = (p < kq) ? min(k / (p + 1), kq) : 0;
+      int incl = len;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (p < kq) rowstart[p] = running + incl - len;
+      running += __shfl_sync(kFull, incl, 31);
+    }
+  }
+  __syncthreads();
+  for (int p = warp; p < kq; p += nwarps) {
+    const int len = min(k / (p + 1), kq);
+    const int rs = rowstart[p];
+    for (int q = lane; q < len; q += 32) pq[rs + q] = (static_cast<uint32_t>(p) << 16) | static_cast<uint32_t>(q);
+  }
+  __syncthreads();
+
+  unsigned char* wbase = smem + L.cta_bytes + warp * L.warp_bytes;
+  float* va = reinterpret_cast<float*>(wbase);  // index order
+  float* vb = va + nkp;
+  float* sa = reinterpret_cast<float*>(wbase + L.off_sorted);  // sorted, descending
+  float* sb = sa + nkp;
+  uint16_t* ia = reinterpret_cast<uint16_t*>(wbase + L.off_ids);
+  uint16_t* ib = ia + nkp;
+  uint64_t* win = reinterpret_cast<uint64_t*>(wbase + L.off_win);
+  uint32_t* cs = reinterpret_cast<uint32_t*>(wbase + L.off_cs);
+  constexpr int LOW = OrdLowBits<T>::value;
+  int nsteps = 0;  // binary-search steps covering [0, nk]
+  while ((1 << nsteps) <= nk) ++nsteps;
+
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * nwarps + warp; t < ntok;
+       t += static_cast<int64_t>(gridDim.x) * nwarps) {
+    const T* a_row = logp + t * nk;
+    const T* b_row = logp + (ntok + t) * nk;
+    // 1. load, keep the index-order copy, sort both halves in registers
+    K ka[E], kb[E];
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int i = (r << 5) | lane;
+      if (i < nk) {
+        const float a = to_f32<T>(a_row[i]) + 0.0f;
+        const float b = to_f32<T>(b_row[i]) + 0.0f;
+        va[i] = a;
+        vb[i] = b;
+        ka[r] = HK::make(a, i);
+        kb[r] = HK::make(b, i);
+      } else {
+        ka[r] = 0;
+        kb[r] = 0;
+      }
+    }
+    bitonic_desc_regs<E, K>(ka, lane);
+    bitonic_desc_regs<E, K>(kb, lane);
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int i = (r << 5) | lane;
+      sa[i] = HK::value(ka[r]);
+      sb[i] = HK::value(kb[r]);
+      ia[i] = static_cast<uint16_t>(HK::id(ka[r]));
+      ib[i] = static_cast<uint16_t>(HK::id(kb[r]));
+    }
+    __syncwarp();
+
+    // 2. staircase candidate scores; track the smallest to narrow the threshold search
+    uint32_t cmin = 0xFFFFFFFFu;
+    for (int c = lane; c < C; c += 32) {
+      const uint32_t e = pq[c];
+      const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(sa[e >> 16], sb[e & 0xFFFFu])) + 0.0f);
+      cs[c] = o;
+      cmin = min(cmin, o);
+    }
+    cmin = __reduce_min_sync(kFull, cmin);
+    __syncwarp();
+    const uint32_t cmax = cs[0];  // ranks (0, 0): the largest sum
+
+    // 3. tau = k-th largest candidate; all candidates agree on the bits above the top differing one
+    uint32_t tau = cmax;
+    if (cmax != cmin) {
+      const int top = 31 - __clz(cmax ^ cmin);
+      tau = cmax & ~((2u << top) - 1u);
+      for (int bit = top; bit >= LOW; --bit) {
+        const uint32_t trial = tau | (1u << bit);
+        int n_ge = 0;
+        for (int c = lane; c < C; c += 32) n_ge += (cs[c] >= trial) ? 1 : 0;
+        n_ge = __reduce_add_sync(kFull, n_ge);
+        if (n_ge >= k) tau = trial;
+      }
+      if (LOW > 0 && (tau >> 31) == 0) tau |= (1u << LOW) - 1u;
+    }
+
+    int filled = 0;
+    for (int base = 0; base < C; base += 32) {
+      const int c = base + lane;
+      const bool g = (c < C) && (cs[c] > tau);
+      const unsigned bal = __ballot_sync(kFull, g);
+      if (g) {
+        const int pos = filled + __popc(bal & ((1u << lane) - 1u));
+        const uint32_t e = pq[c];
+        const uint32_t flat = static_cast<uint32_t>(ia[e >> 16]) * static_cast<uint32_t>(nk) + ib[e & 0xFFFFu];
+        if (pos < k) win[pos] = make_key(cs[c], flat);
+      }
+      filled += __popc(bal);
+    }
+    int need = k - filled;
+
+    // 4. ties with tau: row i = r*32 + lane ties with sorted-b positions [gt, ge); the E rows of a
+    //    lane are searched in lock step so their shared-memory loads overlap
+    int lo_ge[E], hi_ge[E], lo_gt[E], hi_gt[E];
+    float arow[E];
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int i = (r << 5) | lane;
+      arow[r] = (i < nk) ? va[i] : 0.f;
+      lo_ge[r] = 0; hi_ge[r] = (i < nk) ? nk : 0;
+      lo_gt[r] = 0; hi_gt[r] = (i < nk) ? nk : 0;
+    }
+    for (int step = 0; step < nsteps; ++step) {
+#pragma unroll
+      for (int r = 0; r < E; ++r) {
+        if (lo_ge[r] < hi_ge[r]) {
+          const int mid = (lo_ge[r] + hi_ge[r]) >> 1;
+          const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(arow[r], sb[mid])) + 0.0f);
+          if (o >= tau) lo_ge[r] = mid + 1; else hi_ge[r] = mid;
+        }
+        if (lo_gt[r] < hi_gt[r]) {
+          const int mid = (lo_gt[r] + hi_gt[r]) >> 1;
+          const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(arow[r], sb[mid])) + 0.0f);
+          if (o > tau) lo_gt[r] = mid + 1; else hi_gt[r] = mid;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int cnt = lo_ge[r] - lo_gt[r];
+      unsigned has = __ballot_sync(kFull, cnt > 0);
+      while (has != 0 && need > 0) {
+        const int row = (r << 5) + __ffs(has) - 1;
+        has &= has - 1;
+        const float a = va[row];
+        for (int jb = 0; jb < nk && need > 0; jb += 32) {
+          const int j = jb + lane;
+          const bool tie = (j < nk) && (f32_to_ord(round_to<T>(__fadd_rn(a, vb[j])) + 0.0f) == tau);
+          const unsigned bal = __ballot_sync(kFull, tie);
+          const int rank = __popc(bal & ((1u << lane) - 1u));
+          if (tie && rank < need)
+            win[filled + rank] = make_key(tau, static_cast<uint32_t>(row) * static_cast<uint32_t>(nk) + j);
+          const int took = min(__popc(bal), need);
+          filled += took;
+          need -= took;
+        }
+      }
+    }
+    for (int r = filled + lane; r < kp; r += 32) win[r] = 0;
+    __syncwarp();
+
+    // 5. order the winners (registers when they fit, shared memory otherwise) and write out
+    if (kp <= 32) {
+      uint64_t w[1] = {lane < kp ? win[lane] : 0};
+      bitonic_desc_regs<1, uint64_t>(w, lane);
+      if (lane < kp) win[lane] = w[0];
+    } else if (kp == 64) {
+      uint64_t w[2] = {win[lane], win[32 + lane]};
+      bitonic_desc_regs<2, uint64_t>(w, lane);
+      win[lane] = w[0]; win[32 + lane] = w[1];
+    } else if (kp == 128) {
+      uint64_t w[4] = {win[lane], win[32 + lane], win[64 + lane], win[96 + lane]};
+      bitonic_desc_regs<4, uint64_t>(w, lane);
+      win[lane] = w[0]; win[32 + lane] = w[1]; win[64 + lane] = w[2]; win[96 + lane] = w[3];
+    } else {
+      bitonic_desc(win, nullptr, kp, lane);
+    }
+    __syncwarp();
+    float gsum = 0.f;
+    for (int r = lane; r < k; r += 32) {
+      const uint64_t key = win[r];
+      const float s = key_val(key);
+      scores[t * k + r] = from_f32<T>(s);
+      indices[t * k + r] = static_cast<int64_t>(key_id(key));
+      if (gates != nullptr) {
+        const T g = from_f32<T>(expf(s));
+        gsum += to_f32<T>(g);
+        if (!norm) gates[t * k + r] = g;
+      }
+    }
+    if (gates != nullptr && norm) {
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) gsum += __shfl_xor_sync(kFull, gsum, d);
+      const float denom = round_to<T>(gsum);
+      for (int r = lane; r < k; r += 32) {
+        const float g = round_to<T>(expf(key_val(win[r])));
+        gates[t * k + r] = from_f32<T>(g / denom);
+      }
+    }
+    __syncwarp();
+  }
+}
+
+RouterRegLayout make_reg_layout(int nk, int k) {
+  RouterRegLayout L{};
+  L.nkp = next_pow2(nk) < 32 ? 32 : next_pow2(nk);
+  L.kp = next_pow2(k);
+  L.kq = k < nk ? k : nk;
+  int C = 0;
+  for (int p = 0; p < L.kq; ++p) C += (k / (p + 1) < L.kq) ? k / (p + 1) : L.kq;
+  L.C = C;
+  L.Cp = (C + 3) / 4 * 4;
+  L.cta_bytes = static_cast<int>(align_up(static_cast<size_t>(L.Cp) * 4 + static_cast<size_t>(L.kq) * 4, 16));
+  int off = 2 * L.nkp * 4;
+  L.off_sorted = off;
+  off += 2 * L.nkp * 4;
+  L.off_ids = off;
+  off += 2 * L.nkp * 2;
+  off = static_cast<int>(align_up(off, 16));
+  L.off_win = off;
+  off += (L.kp < 32 ? 32 : L.kp) * 8;
+  L.off_cs = off;
+  off += L.Cp * 4;
+  L.warp_bytes = static_cast<int>(align_up(off, 16));
+  return L;
+}
+
+template <typename T, int E>
+int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayout& L, int warps, void* scores,
+               int64_t* indices, void* gates, int norm, cudaStream_t stream) {
+  const int smem = L.cta_bytes + warps * L.warp_bytes;
+  auto kern = router_topk_reg_kernel<T, E>;
+  FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int per_sm = 1;
+  FMOE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, smem));
+  if (per_sm < 1) per_sm = 1;
+  const int64_t want = (T_ + warps - 1) / warps;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * per_sm;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  kern<<<grid, warps * 32, smem, stream>>>(static_cast<const T*>(logp), T_, nk, k, L, static_cast<T*>(scores), indices,
+                                           static_cast<T*>(gates), norm);
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+// register kernel when the halves fit 32 keys per lane and the per-warp scratch stays small
+template <typename T>
+int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int64_t* indices, void* gates, int norm,
+                 cudaStream_t stream);
+
 RouterSmemLayout make_layout(int nk, int k) {
   RouterSmemLayout L{};
   L.nkp = next_pow2(nk);
@@ -257,7 +602,7 @@ RouterSmemLayout make_layout(int nk, int k) {
 }
 
 template <typename T>
-int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int64_t* indices, void* gates, int norm,
+int launch_smem(const void* logp, int64_t T_, int nk, int k, void* scores, int64_t* indices, void* gates, int norm,
                  cudaStream_t stream) {
   const RouterSmemLayout L = make_layout(nk, k);
   constexpr int kMaxSmem = 227 * 1024;
@@ -265,7 +610,7 @@ int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int6
   while (warps > 1 && L.cta_bytes + warps * L.warp_bytes > kMaxSmem / 2) warps >>= 1;  // keep >= 2 CTAs/SM if possible
   if (L.cta_bytes + warps * L.warp_bytes > kMaxSmem) return FMOE_ERR_UNSUPPORTED;
   const int smem = L.cta_bytes + warps * L.warp_bytes;
-  auto kern = router_topk_kernel<T>;
+  auto kern = router_topk_smem_kernel<T>;
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int per_sm = 1;
   FMOE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, smem));
@@ -277,6 +622,30 @@ int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int6
                                            static_cast<T*>(gates), norm);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
+}
+
+
+template <typename T>
+int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int64_t* indices, void* gates, int norm,
+                 cudaStream_t stream) {
+  if (nk <= 1024) {
+    const RouterRegLayout L = make_reg_layout(nk, k);
+    // few tokens per SM: small CTAs spread them over more SMs
+    int warps = 4;
+    while (warps > 1 && L.cta_bytes + warps * L.warp_bytes > 96 * 1024) warps >>= 1;
+    if (L.cta_bytes + warps * L.warp_bytes <= 200 * 1024) {
+      switch (L.nkp / 32) {
+        case 1: return launch_reg<T, 1>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        case 2: return launch_reg<T, 2>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        case 4: return launch_reg<T, 4>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        case 8: return launch_reg<T, 8>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        case 16: return launch_reg<T, 16>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        case 32: return launch_reg<T, 32>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+        default: break;
+      }
+    }
+  }
+  return launch_smem<T>(logp, T_, nk, k, scores, indices, gates, norm, stream);
 }
 
 }  // namespace

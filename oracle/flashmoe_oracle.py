@@ -243,3 +243,41 @@ def rel_rms_error(got: torch.Tensor, want: torch.Tensor) -> float:
     want = want.double()
     rms = want.pow(2).mean().sqrt().item()
     return (got.double() - want).abs().max().item() / max(rms, 1e-30)
+
+
+def output_parity(got: torch.Tensor, want: torch.Tensor, dtype: torch.dtype):
+    """Parity figures for a 16-bit result `got` against the float32 evaluation `want`.
+
+    Returns ``(raw, floor, excess)``, all as multiples of RMS(want):
+    ``raw``    max|got - want| (the budget for bf16 layer outputs is 2e-2);
+    ``floor``  the same figure for `want` itself rounded once to `dtype` - what a perfect
+               implementation that must return `dtype` would score (max|y| * 2^-8 / RMS in the worst
+               case for bf16, so a heavy-tailed output can exceed the budget by rounding alone);
+    ``excess`` the largest error left after discounting, per element, that half-ulp rounding error.
+    """
+    want = want.double()
+    rms = max(want.pow(2).mean().sqrt().item(), 1e-30)
+    err = (got.double() - want).abs()
+    raw = err.max().item() / rms
+    floor = (want.to(dtype).double() - want).abs().max().item() / rms
+    half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    excess = (err - want.abs() * half_ulp).clamp_min(0).max().item() / rms
+    return raw, floor, excess
+
+
+def assert_output_parity(got, want, dtype, raw_budget=2e-2, slack=8e-3, strict=False):
+    """float32: raw < 1e-4.  16-bit: raw < raw_budget, or - when the rounding floor of the output
+    format is itself near or above the budget - raw < floor + slack with nothing but `slack` left
+    beyond the final rounding.  `strict` tightens the slack to 2e-3 (used at the benchmark size)."""
+    if dtype == torch.float32:
+        raw = rel_rms_error(got, want)
+        assert raw < 1e-4, raw
+        return raw
+    raw, floor, excess = output_parity(got.float(), want, dtype)
+    if strict:
+        slack = 2e-3
+    if raw >= raw_budget:
+        assert raw < floor + slack and excess < slack, (
+            f"raw {raw:.3e} x RMS (budget {raw_budget}, rounding floor {floor:.3e}, beyond rounding {excess:.3e})"
+        )
+    return raw

@@ -22,7 +22,7 @@ def run_layer(ours, x, **kw):
     return y.cpu(), logits.cpu(), ours.last_indices.cpu(), ours.last_gates.cpu()
 
 
-def chained_checks(ref, x, y, logits, idx, gates, dtype, out_tol):
+def chained_checks(ref, x, y, logits, idx, gates, dtype, out_tol, strict=False):
     """The parity chain: our logits vs fp32, the reference routing applied to OUR logits, and the
     outputs vs an fp32 evaluation teacher-forced on our indices and gates."""
     T = x.shape[0] * x.shape[1]
@@ -50,9 +50,7 @@ def chained_checks(ref, x, y, logits, idx, gates, dtype, out_tol):
         else:
             assert bf16_ulp_close(gates[rows], want_g[rows], 2).all()
         want_y = ref.forward_fp32_given_routing(x, idx, gates)
-    err = O.rel_rms_error(y.float(), want_y)
-    assert err < out_tol, err
-    return err
+    return O.assert_output_parity(y, want_y, dtype, raw_budget=out_tol, strict=strict)
 
 
 def test_layer_config1_fp32_matches_reference_fixture(golden_dir):
@@ -108,7 +106,7 @@ def test_layer_config2_full_size_bf16():
     ref.eval(); ours.eval()
     x = randn((1, 4096, 1024), 1, torch.bfloat16)
     y, logits, idx, gates = run_layer(ours, x)
-    err = chained_checks(ref, x, y, logits, idx, gates, torch.bfloat16, 2e-2)
+    err = chained_checks(ref, x, y, logits, idx, gates, torch.bfloat16, 2e-2, strict=True)
     print("config 2 teacher-forced error / RMS:", err)
     ours.overlap_shared_mlp = False
     y2, *_ = run_layer(ours, x)
