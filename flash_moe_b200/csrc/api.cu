@@ -232,7 +232,16 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
     if ((rc = mark(stage, end, st)) != FMOE_OK) return rc; \
   } while (0)
 
-  // shared MLP, first half: h = silu(x Wg^T) * (x Wu^T) - independent of routing, may overlap it
+  // router front end: batch-norm -> sub-key GEMM -> log-softmax
+  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 0, s);
+  rc = router_front(a->x, a->router_gate, a->running_mean, a->running_var, a->training, a->bn_momentum, a->bn_eps,
+                    a->router_logits, w.logp, dtype, T, H, nk, w.front, w.front_bytes, a->status, s);
+  if (rc != FMOE_OK) return rc;
+  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
+
+  // shared MLP, first half: h = silu(x Wg^T) * (x Wu^T).  It is independent of routing; on the side
+  // stream it is forked AFTER the router GEMM (both want a whole SM's shared memory) so that the
+  // tensor-core GEMM overlaps the latency-bound top-k and expert gathers that follow.
   ForkJoin* fj = nullptr;
   if (s2 != nullptr && s2 != s) {
     fj = fork_join_events();
@@ -246,12 +255,7 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
     FMOE_CUDA_TRY(cudaEventRecord(fj->join, s2));
   }
 
-  // router: batch-norm -> sub-key GEMM -> log-softmax -> product-key top-k (+ gates)
-  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 0, s);
-  rc = router_front(a->x, a->router_gate, a->running_mean, a->running_var, a->training, a->bn_momentum, a->bn_eps,
-                    a->router_logits, w.logp, dtype, T, H, nk, w.front, w.front_bytes, a->status, s);
-  if (rc != FMOE_OK) return rc;
-  FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
+  // product-key top-k (+ gates)
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 0, s);
   rc = launch_router_topk(w.logp, dtype, T, nk, k, w.scores, indices, gates, a->norm_topk_prob, s);
   if (rc != FMOE_OK) return rc;

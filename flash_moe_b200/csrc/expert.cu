@@ -2,17 +2,20 @@
 //   out[t] = sum_j silu(<x[t], D[e_tj]>) * g[t,j] * U[e_tj]
 // (flash_moe/ops/triton/flash_expert.py:13-211, preprocessing :528-577).
 //
-// Schedule
-//   1. expert-centric order of the (token, slot) pairs by a device-side counting sort
-//      (histogram with warp-aggregated atomics -> exclusive scan -> scatter); no host sync,
-//      ids outside [0, N) are dropped and flagged;
-//   2. scores pass over the SORTED pairs: a warp walks a contiguous run of pairs, keeps the
-//      current expert's down row in registers (loaded once per run of equal ids with 128-bit
-//      loads), gathers each pair's x row, reduces the dot product in fp32 and stores
-//      gs = silu(s) * gate at the pair's original (token, slot) position (4 bytes per pair);
-//      empty experts cost nothing and a hot expert is split over many warps;
-//   3. accumulate pass per token: out[t] = sum_j gs[t,j] * U[e_tj] in fp32 registers, fixed
-//      slot order, one rounding on store - no atomics, run-to-run deterministic.
+// Two schedules, picked by table size
+//   A. tables resident in L2 (16-bit dtypes): no sort.  Scores per token on the tensor cores
+//      (mma.sync, groups of 16 gathered down rows against the token's x row), then the per-token
+//      accumulate of step 3.
+//   B. larger tables (and float32): expert-centric order of the (token, slot) pairs by a
+//      device-side counting sort (histogram with warp-aggregated atomics -> exclusive scan ->
+//      scatter; no host sync; ids outside [0, N) are dropped and flagged), then a scores pass over
+//      the SORTED pairs: a warp walks a contiguous run of pairs, keeps the current expert's down
+//      row in registers (loaded once per run of equal ids with 128-bit loads), gathers each pair's
+//      x row and reduces the dot product in fp32; empty experts cost nothing, a hot expert is
+//      split over many warps.
+//   Both store gs = silu(s) * gate at the pair's (token, slot) position (4 bytes per pair).
+//   3. accumulate pass per token: out[t] = sum_j gs[t,j] * U[e_tj] in fp32 (packed f32x2 FMAs),
+//      fixed slot order, one rounding on store - no atomics, run-to-run deterministic.
 #include "common.cuh"
 
 namespace fmoe {
@@ -240,72 +243,64 @@ template <> struct Mma16816<__half> {
   }
 };
 
+// One warp per (token, group of 16 of its experts); the four warps of a CTA take consecutive
+// groups, so the groups of one token share its x row through L1.  Loads are issued in batches of
+// four 32-column blocks (12 x 16 B per lane in flight) to cover the L2 latency of the gather.
 template <typename T>
 __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restrict__ x, const T* __restrict__ down,
                                                                const int64_t* __restrict__ idx,
                                                                const T* __restrict__ gates, float* __restrict__ gs,
                                                                int64_t ntok, int H, int64_t N, int k,
                                                                int32_t* status) {
+  constexpr int UNROLL = 4;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int groups = (k + 15) >> 4;
+  const int64_t tasks = ntok * groups;
   bool bad = false;
-  for (int64_t t = warp_global; t < ntok; t += warps_total) {
-    const T* xr = x + t * H;
-    for (int j0 = 0; j0 < k; j0 += 64) {
-      const int ngroups = min(4, (k - j0 + 15) >> 4);
-      const T* ra[4];
-      const T* rb[4];
-      bool oka[4], okb[4];
+  for (int64_t task = warp_global; task < tasks; task += warps_total) {
+    const int64_t t = task / groups;
+    const int G = static_cast<int>(task - t * groups);
+    const int ja = G * 16 + g, jb = ja + 8;
+    int64_t ea = 0, eb = 0;
+    if (ja < k) ea = idx[t * k + ja];
+    if (jb < k) eb = idx[t * k + jb];
+    const bool oka = (ja < k) && ea >= 0 && ea < N;
+    const bool okb = (jb < k) && eb >= 0 && eb < N;
+    if ((ja < k && !oka) || (jb < k && !okb)) bad = true;
+    const T* ra = down + (oka ? ea : 0) * H + 8 * tq;
+    const T* rb = down + (okb ? eb : 0) * H + 8 * tq;
+    const T* rx = x + t * H + 8 * tq;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c0 = 0; c0 < H; c0 += 32 * UNROLL) {
+      uint4 xq[UNROLL], qa[UNROLL], qb[UNROLL];
 #pragma unroll
-      for (int G = 0; G < 4; ++G) {
-        const int ja = j0 + G * 16 + g, jb = ja + 8;
-        int64_t ea = 0, eb = 0;
-        if (ja < k) ea = idx[t * k + ja];
-        if (jb < k) eb = idx[t * k + jb];
-        oka[G] = (ja < k) && ea >= 0 && ea < N;
-        okb[G] = (jb < k) && eb >= 0 && eb < N;
-        if ((ja < k && !oka[G]) || (jb < k && !okb[G])) bad = true;
-        ra[G] = down + (oka[G] ? ea : 0) * H;
-        rb[G] = down + (okb[G] ? eb : 0) * H;
+      for (int u = 0; u < UNROLL; ++u) {
+        const int col = c0 + 32 * u;
+        const bool in = col + 8 * tq < H;
+        xq[u] = in ? ldg16(rx + col) : make_uint4(0, 0, 0, 0);
+        qa[u] = in ? ldg16(ra + col) : make_uint4(0, 0, 0, 0);
+        qb[u] = in ? ldg16(rb + col) : make_uint4(0, 0, 0, 0);
       }
-      float c[4][4];
 #pragma unroll
-      for (int G = 0; G < 4; ++G)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) c[G][i] = 0.f;
-#pragma unroll 2
-      for (int c0 = 0; c0 < H; c0 += 32) {
-        const int col = c0 + 8 * tq;
-        const bool in = col < H;
-        const uint4 xq = in ? ldg16(xr + col) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int G = 0; G < 4; ++G) {
-          if (G < ngroups) {
-            const uint4 qa = in ? ldg16(ra[G] + col) : make_uint4(0, 0, 0, 0);
-            const uint4 qb = in ? ldg16(rb[G] + col) : make_uint4(0, 0, 0, 0);
-            Mma16816<T>::run(c[G], qa.x, qb.x, qa.y, qb.y, xq.x, xq.y);
-            Mma16816<T>::run(c[G], qa.z, qb.z, qa.w, qb.w, xq.z, xq.w);
-          }
-        }
+      for (int u = 0; u < UNROLL; ++u) {
+        Mma16816<T>::run(c, qa[u].x, qb[u].x, qa[u].y, qb[u].y, xq[u].x, xq[u].y);
+        Mma16816<T>::run(c, qa[u].z, qb[u].z, qa[u].w, qb[u].w, xq[u].z, xq[u].w);
       }
-      if (tq == 0) {
-#pragma unroll
-        for (int G = 0; G < 4; ++G) {
-          const int ja = j0 + G * 16 + g, jb = ja + 8;
-          if (ja < k) gs[t * k + ja] = oka[G] ? silu_f32(c[G][0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
-          if (jb < k) gs[t * k + jb] = okb[G] ? silu_f32(c[G][2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
-        }
-      }
+    }
+    if (tq == 0) {
+      if (ja < k) gs[t * k + ja] = oka ? silu_f32(c[0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
+      if (jb < k) gs[t * k + jb] = okb ? silu_f32(c[2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
     }
   }
   if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_EXPERT_ID);
 }
 
 // ---------------------------------------------------------------- 3. per-token accumulate
-// One warp per (token, column block of 32*VEC*NCH elements); four gathered rows in flight per
-// lane, packed f32x2 FMAs (two accumulators per instruction).
+// One warp per (token, column block of 32*VEC*NCH elements); 16 x 16 B of gathered rows in flight
+// per lane, packed f32x2 FMAs (two accumulators per instruction).
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -319,11 +314,11 @@ __device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t a, uint64_t b) {
 }
 
 template <typename T, typename OutT, int NCH>
-__global__ void __launch_bounds__(256) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
+__global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
                                                           const float* __restrict__ gs, OutT* __restrict__ out,
                                                           int64_t ntok, int H, int64_t N, int k, int colblocks) {
   constexpr int VEC = Vec16<T>::N;
-  constexpr int SLOTS = 4;
+  constexpr int SLOTS = NCH >= 4 ? 4 : 8;
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -449,10 +444,10 @@ void launch_accum(const void* up, const int64_t* idx, const ExpertWs& w, void* o
   constexpr int VEC = Vec16<T>::N;
   const int colblocks = (H + 32 * VEC * NCH - 1) / (32 * VEC * NCH);
   const int64_t tasks = T_ * colblocks;
-  const int64_t want = (tasks + 7) / 8;
-  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  const int64_t want = (tasks + 3) / 4;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
-  expert_accum_kernel<T, OutT, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(up), idx, w.gs,
+  expert_accum_kernel<T, OutT, NCH><<<grid, 128, 0, stream>>>(static_cast<const T*>(up), idx, w.gs,
                                                               static_cast<OutT*>(out), T_, H, N, k, colblocks);
 }
 
@@ -470,7 +465,7 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
   const bool token_centric = sizeof(T) == 2 && (2.0 * static_cast<double>(N) * H * sizeof(T) <= 96.0 * 1024 * 1024);
   if (token_centric) {
     if constexpr (sizeof(T) == 2) {
-      const int64_t want = (T_ + 3) / 4;
+      const int64_t want = (T_ * ((k + 15) / 16) + 3) / 4;
       const int64_t cap = static_cast<int64_t>(sms) * 16;
       const int grid = static_cast<int>(want < cap ? want : cap);
       expert_scores_mma_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down), idx,
@@ -515,10 +510,9 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
     if (out_f32) launch_accum<T, float, NCH_>(up, idx, w, out, T_, H, N, k, stream);           \
     else launch_accum<T, T, NCH_>(up, idx, w, out, T_, H, N, k, stream);                       \
   } while (0)
+  // narrow column blocks: more warps per token, i.e. more gathers in flight
   if (need <= 1) FMOE_ACCUM(1);
-  else if (need <= 2) FMOE_ACCUM(2);
-  else if (need <= 4) FMOE_ACCUM(4);
-  else FMOE_ACCUM(8);
+  else FMOE_ACCUM(2);
 #undef FMOE_ACCUM
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;

@@ -93,6 +93,7 @@ class FlashMoE(nn.Module):
 
         self.overlap_shared_mlp = overlap_shared_mlp
         self._aux_streams: Dict[int, torch.cuda.Stream] = {}
+        self._workspaces: Dict[int, torch.Tensor] = {}
         self.last_indices: Optional[torch.Tensor] = None
         self.last_gates: Optional[torch.Tensor] = None
 
@@ -101,6 +102,17 @@ class FlashMoE(nn.Module):
         if key not in self._aux_streams:
             self._aux_streams[key] = torch.cuda.Stream(device=dev)
         return self._aux_streams[key]
+
+    def _workspace(self, dev: torch.device, nbytes: int) -> torch.Tensor:
+        """Scratch memory kept by the module and reused by every forward (grown on demand).  Successive
+        forwards issued from one stream are ordered by that stream; callers that drive ONE module
+        instance from several streams at once must synchronise them themselves."""
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        ws = self._workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+            self._workspaces[key] = ws
+        return ws
 
     def kernels_per_forward(self) -> int:
         """Kernels of this library launched by one forward (16-bit dtypes): batch-norm finalize + apply,
@@ -154,7 +166,7 @@ class FlashMoE(nn.Module):
         L = _lib.lib()
         code = _lib.dtype_code(x)
         ws_bytes = L.fmoe_layer_workspace_bytes(T, H, I, N, nk, k, code)
-        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        ws = self._workspace(dev, ws_bytes)
 
         with torch.cuda.device(dev):
             main = torch.cuda.current_stream(dev)
@@ -188,10 +200,8 @@ class FlashMoE(nn.Module):
             a.bn_eps = float(bn.eps)
             rc = L.fmoe_layer_forward(ctypes.byref(a))
         _lib.check(rc, "fmoe_layer_forward")
-        if aux is not None:
-            # the workspace and the inputs were also used on the side stream
-            ws.record_stream(aux)
-            x.record_stream(aux)
+        # The side stream is joined back into the calling stream inside the library call, so the
+        # input, the outputs and the workspace need no cross-stream bookkeeping afterwards.
         if training and bn.num_batches_tracked is not None and self.training:
             bn.num_batches_tracked += 1
         if return_routing:

@@ -137,10 +137,17 @@ def expert_forward_eager(x2d, down_table, up_table, indices, gates) -> torch.Ten
     return torch.matmul(w.view(T, 1, -1), u).view(T, -1)
 
 
-def mlp_forward(x2d, gate_w, up_w, down_w, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` (flash_moe/ops/triton/flash_mlp.py:169-181) evaluated in compute_dtype."""
+def mlp_forward(x2d, gate_w, up_w, down_w, compute_dtype: torch.dtype = torch.float32, round_h_to=None) -> torch.Tensor:
+    """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` (flash_moe/ops/triton/flash_mlp.py:169-181) evaluated in compute_dtype.
+
+    ``round_h_to``: round the intermediate ``h = silu(.) * (.)`` once to that dtype before the down
+    projection, as every implementation that stores h in 16 bits between the two GEMMs does (the
+    reference stores it in the module dtype, flash_mlp.py:46-48,:119).
+    """
     xs = x2d.to(compute_dtype)
     h = F.silu(xs @ gate_w.to(compute_dtype).t()) * (xs @ up_w.to(compute_dtype).t())
+    if round_h_to is not None:
+        h = h.to(round_h_to).to(compute_dtype)
     return h @ down_w.to(compute_dtype).t()
 
 
@@ -199,12 +206,13 @@ class OracleFlashMoE(nn.Module):
         y = (mlp + experts).view(B, S, H)
         return y, logits.view(B * S, 2, self.num_keys).transpose(0, 1)
 
-    def forward_fp32_given_routing(self, hidden_states, indices, gates) -> torch.Tensor:
-        """float32 evaluation of experts + MLP + add on the stored (possibly bf16) operands for a *given* routing."""
+    def forward_fp32_given_routing(self, hidden_states, indices, gates, round_h_to=None) -> torch.Tensor:
+        """float32 evaluation of experts + MLP + add on the stored (possibly bf16) operands for a *given* routing.
+        ``round_h_to`` rounds the MLP intermediate once to that dtype (see `mlp_forward`)."""
         H = hidden_states.shape[-1]
         x2d = hidden_states.reshape(-1, H)
         e = expert_forward(x2d, self.down_embed.weight, self.up_embed.weight, indices, gates)
-        m = mlp_forward(x2d, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        m = mlp_forward(x2d, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, round_h_to=round_h_to)
         return (e + m).view(*hidden_states.shape)
 
 
@@ -268,15 +276,15 @@ def output_parity(got: torch.Tensor, want: torch.Tensor, dtype: torch.dtype):
 def assert_output_parity(got, want, dtype, raw_budget=2e-2, slack=8e-3, strict=False):
     """float32: raw < 1e-4.  16-bit: raw < raw_budget, or - when the rounding floor of the output
     format is itself near or above the budget - raw < floor + slack with nothing but `slack` left
-    beyond the final rounding.  `strict` tightens the slack to 2e-3 (used at the benchmark size)."""
+    beyond the final rounding.  `strict` always applies the floor test, with the slack tightened to 3e-3."""
     if dtype == torch.float32:
         raw = rel_rms_error(got, want)
         assert raw < 1e-4, raw
         return raw
     raw, floor, excess = output_parity(got.float(), want, dtype)
     if strict:
-        slack = 2e-3
-    if raw >= raw_budget:
+        slack = 3e-3
+    if raw >= raw_budget or strict:
         assert raw < floor + slack and excess < slack, (
             f"raw {raw:.3e} x RMS (budget {raw_budget}, rounding floor {floor:.3e}, beyond rounding {excess:.3e})"
         )

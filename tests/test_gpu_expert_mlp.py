@@ -112,13 +112,14 @@ def test_mlp_forward(T, H, I, dtype):
     wu = randn((I, H), 3, dtype, 1.0 / H**0.5)
     wd = randn((H, I), 4, dtype, 1.0 / I**0.5)
     add = randn((T, H), 5, torch.float32, 0.3)
-    want = O.mlp_forward(x, wg, wu, wd)
+    # 16-bit: the intermediate h lives in the storage dtype between the two GEMMs (as in the reference)
+    want = O.mlp_forward(x, wg, wu, wd, round_h_to=None if dtype == torch.float32 else dtype)
     got = flash_mlp_func(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
     got_add = flash_mlp_add(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), add.cuda())
     again = flash_mlp_func(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
     check_status()
-    O.assert_output_parity(got.cpu(), want, dtype)
-    O.assert_output_parity(got_add.cpu(), want + add, dtype)
+    O.assert_output_parity(got.cpu(), want, dtype, strict=True)
+    O.assert_output_parity(got_add.cpu(), want + add, dtype, strict=True)
     assert torch.equal(got, again)
 
 
