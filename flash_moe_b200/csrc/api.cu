@@ -58,12 +58,13 @@ size_t router_front_ws(int64_t T, int H, int dtype) {
   return c.off;
 }
 
+// logp == nullptr: stop after the logits (the caller applies the log-softmax elsewhere)
 int router_front(const void* x, const void* w, void* rm, void* rv, int training, float momentum, float eps,
                  void* logits, void* logp, int dtype, int64_t T, int H, int nk, void* ws, size_t ws_bytes,
                  int32_t* status, cudaStream_t stream) {
   if (!valid_dtype(dtype) || T < 0 || H <= 0 || nk <= 0) return FMOE_ERR_BAD_ARG;
   if (T == 0) return FMOE_OK;
-  if (x == nullptr || w == nullptr || logits == nullptr || logp == nullptr) return FMOE_ERR_BAD_ARG;
+  if (x == nullptr || w == nullptr || logits == nullptr) return FMOE_ERR_BAD_ARG;
   if (ws == nullptr || ws_bytes < router_front_ws(T, H, dtype)) return FMOE_ERR_WORKSPACE;
   Carver c(ws);
   void* xn = c.take(static_cast<size_t>(T) * H * dtype_size(dtype));
@@ -71,7 +72,7 @@ int router_front(const void* x, const void* w, void* rm, void* rv, int training,
   int rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, stream);
   if (rc != FMOE_OK) return rc;
   const bool tc = is16(dtype) && (H % 8 == 0) && aligned16(w);
-  if (tc && gemm_router_fused_supported(nk) && aligned16(logits) && aligned16(logp))
+  if (logp != nullptr && tc && gemm_router_fused_supported(nk) && aligned16(logits) && aligned16(logp))
     return launch_gemm_router(xn, H, 0, w, logits, logp, dtype, T, nk, H, status, stream);
   if (tc && (2 * nk) % 8 == 0 && aligned16(logits))
     rc = launch_gemm_add(xn, w, nullptr, logits, dtype, T, 2 * nk, H, status, stream);
@@ -79,6 +80,7 @@ int router_front(const void* x, const void* w, void* rm, void* rv, int training,
     rc = launch_simt_gemm(xn, H, w, nullptr, nullptr, logits, 2 * static_cast<int64_t>(nk), dtype, 0, T, 2 * nk, H,
                           stream);
   if (rc != FMOE_OK) return rc;
+  if (logp == nullptr) return FMOE_OK;
   return launch_log_softmax_halves(logits, logp, dtype, T, nk, stream);
 }
 
@@ -145,8 +147,8 @@ const char* fmoe_error_string(int code) {
 
 int fmoe_router_topk(const void* log_probs, int dtype, int64_t num_tokens, int num_keys, int top_k, void* scores,
                      int64_t* indices, void* gates, int norm_topk_prob, fmoe_stream_t stream) {
-  return launch_router_topk(log_probs, dtype, num_tokens, num_keys, top_k, scores, indices, gates, norm_topk_prob,
-                            static_cast<cudaStream_t>(stream));
+  return launch_router_topk(log_probs, dtype, num_tokens, num_keys, top_k, scores, indices, gates,
+                            norm_topk_prob ? 1 : 0, static_cast<cudaStream_t>(stream));
 }
 
 size_t fmoe_router_front_workspace_bytes(int64_t num_tokens, int hidden, int num_keys, int dtype) {
@@ -159,6 +161,7 @@ int fmoe_router_front(const void* x, const void* router_weight, void* running_me
                       float momentum, float eps, void* logits, void* log_probs, int dtype, int64_t num_tokens,
                       int hidden, int num_keys, void* workspace, size_t workspace_bytes, int32_t* status,
                       fmoe_stream_t stream) {
+  if (log_probs == nullptr && num_tokens > 0) return FMOE_ERR_BAD_ARG;
   return router_front(x, router_weight, running_mean, running_var, training, momentum, eps, logits, log_probs, dtype,
                       num_tokens, hidden, num_keys, workspace, workspace_bytes, status,
                       static_cast<cudaStream_t>(stream));
@@ -232,10 +235,14 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
     if ((rc = mark(stage, end, st)) != FMOE_OK) return rc; \
   } while (0)
 
-  // router front end: batch-norm -> sub-key GEMM -> log-softmax
+  // router front end: batch-norm -> sub-key GEMM.  For 16-bit dtypes and num_keys <= 1024 the top-k
+  // kernel applies the per-half log-softmax itself (each warp already holds both halves of its
+  // token in registers), which saves a [2, T, nk] round trip and a serial GEMM epilogue.
+  const bool topk_from_logits = is16(dtype) && nk <= 1024;
   FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 0, s);
   rc = router_front(a->x, a->router_gate, a->running_mean, a->running_var, a->training, a->bn_momentum, a->bn_eps,
-                    a->router_logits, w.logp, dtype, T, H, nk, w.front, w.front_bytes, a->status, s);
+                    a->router_logits, topk_from_logits ? nullptr : w.logp, dtype, T, H, nk, w.front, w.front_bytes,
+                    a->status, s);
   if (rc != FMOE_OK) return rc;
   FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
 
@@ -257,7 +264,17 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
 
   // product-key top-k (+ gates)
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 0, s);
-  rc = launch_router_topk(w.logp, dtype, T, nk, k, w.scores, indices, gates, a->norm_topk_prob, s);
+  rc = FMOE_ERR_UNSUPPORTED;
+  if (topk_from_logits)
+    rc = launch_router_topk(a->router_logits, dtype, T, nk, k, w.scores, indices, gates,
+                            (a->norm_topk_prob ? 1 : 0) | 2, s);
+  if (rc == FMOE_ERR_UNSUPPORTED) {
+    if (topk_from_logits) {  // shapes the register kernel does not cover: explicit log-softmax pass
+      rc = launch_log_softmax_halves(a->router_logits, w.logp, dtype, T, nk, s);
+      if (rc != FMOE_OK) return rc;
+    }
+    rc = launch_router_topk(w.logp, dtype, T, nk, k, w.scores, indices, gates, a->norm_topk_prob ? 1 : 0, s);
+  }
   if (rc != FMOE_OK) return rc;
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 1, s);
   FMOE_MARK(FMOE_STAGE_EXPERTS, 0, s);

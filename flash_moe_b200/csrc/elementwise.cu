@@ -64,20 +64,37 @@ __global__ void bn_finalize_kernel(const float* __restrict__ psum, const float* 
   invstd_out[c] = 1.0f / sqrtf(var + eps);
 }
 
+// blockIdx.x / threadIdx.x pick a fixed group of VEC columns (mean / inv-std stay in registers),
+// blockIdx.y strides over the rows; consecutive threads read consecutive 16-byte pieces of a row.
 template <typename T>
-__global__ void bn_apply_kernel(const T* __restrict__ x, T* __restrict__ xn, const float* __restrict__ mean,
-                                const float* __restrict__ invstd, int64_t ntok, int H) {
+__global__ void __launch_bounds__(128) bn_apply_kernel(const T* __restrict__ x, T* __restrict__ xn,
+                                                      const float* __restrict__ mean,
+                                                      const float* __restrict__ invstd, int64_t ntok, int H) {
   constexpr int VEC = Vec16<T>::N;
-  const int64_t nvec = ntok * H / VEC;
-  const int hv = H / VEC;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int c0 = static_cast<int>(i % hv) * VEC;
-    float f[VEC];
-    unpack16<T>(ldg16(x + i * VEC), f);
+  const int cv = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cv * VEC >= H) return;
+  float m[VEC], s[VEC];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) f[j] = (f[j] - __ldg(mean + c0 + j)) * __ldg(invstd + c0 + j);
-    *reinterpret_cast<uint4*>(xn + i * VEC) = pack16<T>(f);
+  for (int j = 0; j < VEC; ++j) {
+    m[j] = mean[cv * VEC + j];
+    s[j] = invstd[cv * VEC + j];
+  }
+  constexpr int ROWS = 4;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * ROWS; r0 < ntok; r0 += static_cast<int64_t>(gridDim.y) * ROWS) {
+    uint4 q[ROWS];
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u)
+      q[u] = (r0 + u < ntok) ? ldg16(x + (r0 + u) * H + cv * VEC) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+      if (r0 + u < ntok) {
+        float f[VEC];
+        unpack16<T>(q[u], f);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f[j] = (f[j] - m[j]) * s[j];
+        *reinterpret_cast<uint4*>(xn + (r0 + u) * H + cv * VEC) = pack16<T>(f);
+      }
+    }
   }
 }
 
@@ -121,10 +138,13 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
                                                             training, momentum, eps, ntok, H, mean, invstd);
   FMOE_LAUNCH_CHECK();
   constexpr int VEC = Vec16<T>::N;
-  const int64_t nvec = ntok * H / VEC;
-  const int64_t want = (nvec + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
-  bn_apply_kernel<T><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+  const int hv = H / VEC;
+  const int gx = (hv + 127) / 128;
+  int64_t gy = (ntok + 3) / 4;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16 / gx;
+  if (gy > cap) gy = cap > 0 ? cap : 1;
+  if (gy > 65535) gy = 65535;
+  bn_apply_kernel<T><<<dim3(gx, static_cast<unsigned>(gy)), 128, 0, stream>>>(
       static_cast<const T*>(x), static_cast<T*>(xn), mean, invstd, ntok, H);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;

@@ -208,9 +208,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       } else if constexpr (EPI == EPI_ADD) {
         T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
-        const float* arow = ep.addend ? ep.addend + row * ep.ldo : nullptr;
+        const float* arow = (ep.addend != nullptr && row_ok) ? ep.addend + row * ep.ldo : nullptr;
+        constexpr int NCHUNK = BLOCK_N / 32;
+        // the fp32 addend of the next 32 columns is fetched while the current chunk is processed
+        float4 nxt[8];
+        auto fetch = [&](int c) {
+          const int col0 = n_tile * BLOCK_N + c * 32;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            nxt[v] = (arow != nullptr && col0 + v * 4 < ep.n_valid)
+                         ? __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 4))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        fetch(0);
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
+        for (int c = 0; c < NCHUNK; ++c) {
+          float4 cur[8];
+#pragma unroll
+          for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
+          if (c + 1 < NCHUNK) fetch(c + 1);
           uint32_t a[32];
           ptx::tmem_ld_32x32(taddr + c * 32, a);
           ptx::tmem_ld_wait();
@@ -222,12 +238,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
-                if (arow != nullptr) {
-                  const float4 p0 = __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 8));
-                  const float4 p1 = __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 8 + 4));
-                  f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w;
-                  f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
-                }
+                f[0] += cur[2 * v].x; f[1] += cur[2 * v].y; f[2] += cur[2 * v].z; f[3] += cur[2 * v].w;
+                f[4] += cur[2 * v + 1].x; f[5] += cur[2 * v + 1].y; f[6] += cur[2 * v + 1].z; f[7] += cur[2 * v + 1].w;
                 *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
               }
             }
@@ -401,7 +413,9 @@ int launch_gemm_add(const void* a, const void* b, const float* addend, void* out
   CUtensorMap tA, tB;
   if ((rc = make_tmap(&tA, a, dtype, K, M, K, BLOCK_M)) != FMOE_OK) return rc;
   EpiParams ep{out, nullptr, addend, N, N, 0};
-  if (N > 128) {
+  const int64_t m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
+  const bool wide = N > 128 && m_tiles * ((N + 255) / 256) * 2 > device_sm_count();
+  if (wide) {
     if ((rc = make_tmap(&tB, b, dtype, K, N, K, 256)) != FMOE_OK) return rc;
     const int n_tiles = (N + 255) / 256;
     if (dtype == FMOE_DTYPE_BF16)
@@ -409,9 +423,10 @@ int launch_gemm_add(const void* a, const void* b, const float* addend, void* out
     return launch<256, EPI_ADD, __half>(tA, tB, tB, ep, M, n_tiles, K, status, stream);
   }
   if ((rc = make_tmap(&tB, b, dtype, K, N, K, 128)) != FMOE_OK) return rc;
+  const int n_tiles = (N + 127) / 128;
   if (dtype == FMOE_DTYPE_BF16)
-    return launch<128, EPI_ADD, __nv_bfloat16>(tA, tB, tB, ep, M, 1, K, status, stream);
-  return launch<128, EPI_ADD, __half>(tA, tB, tB, ep, M, 1, K, status, stream);
+    return launch<128, EPI_ADD, __nv_bfloat16>(tA, tB, tB, ep, M, n_tiles, K, status, stream);
+  return launch<128, EPI_ADD, __half>(tA, tB, tB, ep, M, n_tiles, K, status, stream);
 }
 
 bool gemm_router_fused_supported(int nk) { return nk >= 1 && nk <= 256; }

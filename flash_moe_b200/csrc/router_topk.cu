@@ -316,7 +316,9 @@ template <typename T, int E>
 __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restrict__ logp, int64_t ntok, int nk, int k,
                                                              RouterRegLayout L, T* __restrict__ scores,
                                                              int64_t* __restrict__ indices, T* __restrict__ gates,
-                                                             int norm) {
+                                                             int flags) {
+  const int norm = flags & 1;
+  const bool from_logits = (flags & 2) != 0;
   using HK = HalfKey<T>;
   using K = typename HK::type;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -365,16 +367,52 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
 
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * nwarps + warp; t < ntok;
        t += static_cast<int64_t>(gridDim.x) * nwarps) {
-    const T* a_row = logp + t * nk;
-    const T* b_row = logp + (ntok + t) * nk;
+    // from_logits: the input is the raw router logits [T, 2*nk]; the per-half log-softmax
+    // (flash_moe/modules/flash_moe.py:72) is applied here, rounded to T like torch does
+    const T* a_row = from_logits ? logp + t * 2 * nk : logp + t * nk;
+    const T* b_row = from_logits ? a_row + nk : logp + (ntok + t) * nk;
     // 1. load, keep the index-order copy, sort both halves in registers
     K ka[E], kb[E];
+    float la[E], lb[E];
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int i = (r << 5) | lane;
+      la[r] = (i < nk) ? to_f32<T>(a_row[i]) : -INFINITY;
+      lb[r] = (i < nk) ? to_f32<T>(b_row[i]) : -INFINITY;
+    }
+    if (from_logits) {
+      float ma = -INFINITY, mb = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < E; ++r) { ma = fmaxf(ma, la[r]); mb = fmaxf(mb, lb[r]); }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        ma = fmaxf(ma, __shfl_xor_sync(kFull, ma, d));
+        mb = fmaxf(mb, __shfl_xor_sync(kFull, mb, d));
+      }
+      float sa_ = 0.f, sb_ = 0.f;
+#pragma unroll
+      for (int r = 0; r < E; ++r) {
+        const int i = (r << 5) | lane;
+        if (i < nk) { sa_ += expf(la[r] - ma); sb_ += expf(lb[r] - mb); }
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        sa_ += __shfl_xor_sync(kFull, sa_, d);
+        sb_ += __shfl_xor_sync(kFull, sb_, d);
+      }
+      const float lga = logf(sa_), lgb = logf(sb_);
+#pragma unroll
+      for (int r = 0; r < E; ++r) {
+        la[r] = round_to<T>((la[r] - ma) - lga);
+        lb[r] = round_to<T>((lb[r] - mb) - lgb);
+      }
+    }
 #pragma unroll
     for (int r = 0; r < E; ++r) {
       const int i = (r << 5) | lane;
       if (i < nk) {
-        const float a = to_f32<T>(a_row[i]) + 0.0f;
-        const float b = to_f32<T>(b_row[i]) + 0.0f;
+        const float a = la[r] + 0.0f;
+        const float b = lb[r] + 0.0f;
         va[i] = a;
         vb[i] = b;
         ka[r] = HK::make(a, i);
@@ -645,11 +683,13 @@ int launch_typed(const void* logp, int64_t T_, int nk, int k, void* scores, int6
       }
     }
   }
+  if (norm & 2) return FMOE_ERR_UNSUPPORTED;  // raw logits are only accepted by the register kernel
   return launch_smem<T>(logp, T_, nk, k, scores, indices, gates, norm, stream);
 }
 
 }  // namespace
 
+// norm: bit 0 = renormalise the gates per token, bit 1 = `log_probs` holds raw logits [T, 2*nk]
 int launch_router_topk(const void* log_probs, int dtype, int64_t T, int nk, int k, void* scores, int64_t* indices,
                        void* gates, int norm, cudaStream_t stream) {
   if (T < 0 || nk <= 0 || k < 0 || k > nk) return FMOE_ERR_BAD_ARG;
