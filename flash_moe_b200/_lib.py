@@ -77,6 +77,8 @@ SIGNATURES = {
     "fmoe_router_front": (_I, [_P, _P, _P, _P, _I, _F, _F, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
+    "fmoe_expert_static_scratch_bytes": (_Z, []),
+    "fmoe_expert_forward_static": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _P]),
     "fmoe_mlp_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fmoe_mlp_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_layer_workspace_bytes": (_Z, [_L, _I, _I, _L, _I, _I, _I]),

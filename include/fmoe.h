@@ -94,6 +94,22 @@ int fmoe_expert_forward(const void* x, const void* down, const void* up, const i
                         int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * fmoe_expert_forward without a caller-supplied workspace.  It has no counterpart in the
+ * reference; it exists for hosts that cannot allocate device memory where they call the library
+ * (a frozen memory plan after warm-up, a fixed real-time budget, a language binding without a
+ * device allocator).  Same arguments and results as fmoe_expert_forward; the scratch is a
+ * fmoe_expert_static_scratch_bytes() = 8 MiB array inside the library image that each GPU using
+ * the library holds until the process exits.  Shapes with fmoe_expert_workspace_bytes(...) above
+ * that limit return FMOE_ERR_WORKSPACE.  All calls share the array: calls that overlap on the GPU
+ * race, so order them on one stream or with events.  The first call on a device looks up the
+ * array's device address and should be made outside any stream capture.  Nothing is allocated.
+ */
+size_t fmoe_expert_static_scratch_bytes(void);
+int fmoe_expert_forward_static(const void* x, const void* down, const void* up, const int64_t* indices,
+                               const void* gates, void* out, int dtype, int out_dtype, int64_t num_tokens, int hidden,
+                               int64_t num_experts, int top_k, int32_t* status, fmoe_stream_t stream);
+
+/*
  * Shared SwiGLU MLP: out = (silu(x Wg^T) * (x Wu^T)) Wd^T  (+ addend).
  * Replaces triton_flash_mlp_func(x, gate_weight, up_weight, down_weight)
  *   flash_moe/ops/triton/flash_mlp.py:169-181 and the final add flash_moe/modules/flash_moe.py:101.
