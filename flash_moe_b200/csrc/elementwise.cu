@@ -69,15 +69,23 @@ __global__ void bn_finalize_kernel(const float* __restrict__ psum, const float* 
 template <typename T>
 __global__ void __launch_bounds__(128) bn_apply_kernel(const T* __restrict__ x, T* __restrict__ xn,
                                                       const float* __restrict__ mean,
-                                                      const float* __restrict__ invstd, int64_t ntok, int H) {
+                                                      const float* __restrict__ invstd,
+                                                      const T* __restrict__ running_mean,
+                                                      const T* __restrict__ running_var, float eps, int64_t ntok,
+                                                      int H) {
   constexpr int VEC = Vec16<T>::N;
   const int cv = blockIdx.x * blockDim.x + threadIdx.x;
   if (cv * VEC >= H) return;
   float m[VEC], s[VEC];
 #pragma unroll
   for (int j = 0; j < VEC; ++j) {
-    m[j] = mean[cv * VEC + j];
-    s[j] = invstd[cv * VEC + j];
+    if (running_mean != nullptr) {  // eval mode: statistics straight from the running buffers
+      m[j] = to_f32<T>(running_mean[cv * VEC + j]);
+      s[j] = 1.0f / sqrtf(to_f32<T>(running_var[cv * VEC + j]) + eps);
+    } else {
+      m[j] = mean[cv * VEC + j];
+      s[j] = invstd[cv * VEC + j];
+    }
   }
   constexpr int ROWS = 4;
   for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * ROWS; r0 < ntok; r0 += static_cast<int64_t>(gridDim.y) * ROWS) {
@@ -134,9 +142,11 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
     bn_partial_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), ntok, H, psum, psq);
     FMOE_LAUNCH_CHECK();
   }
-  bn_finalize_kernel<T><<<(H + 127) / 128, 128, 0, stream>>>(psum, psq, static_cast<T*>(rm), static_cast<T*>(rv),
-                                                            training, momentum, eps, ntok, H, mean, invstd);
-  FMOE_LAUNCH_CHECK();
+  if (training) {
+    bn_finalize_kernel<T><<<(H + 127) / 128, 128, 0, stream>>>(psum, psq, static_cast<T*>(rm), static_cast<T*>(rv),
+                                                              training, momentum, eps, ntok, H, mean, invstd);
+    FMOE_LAUNCH_CHECK();
+  }
   constexpr int VEC = Vec16<T>::N;
   const int hv = H / VEC;
   const int gx = (hv + 127) / 128;
@@ -145,7 +155,8 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
   if (gy > cap) gy = cap > 0 ? cap : 1;
   if (gy > 65535) gy = 65535;
   bn_apply_kernel<T><<<dim3(gx, static_cast<unsigned>(gy)), 128, 0, stream>>>(
-      static_cast<const T*>(x), static_cast<T*>(xn), mean, invstd, ntok, H);
+      static_cast<const T*>(x), static_cast<T*>(xn), mean, invstd, training ? nullptr : static_cast<const T*>(rm),
+      training ? nullptr : static_cast<const T*>(rv), eps, ntok, H);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }

@@ -92,10 +92,13 @@ __global__ void router_topk_smem_kernel(const T* __restrict__ logp, int64_t ntok
     }
   }
   __syncthreads();
-  for (int p = warp; p < kq; p += nwarps) {
-    const int len = min(k / (p + 1), kq);
-    const int rs = rowstart[p];
-    for (int q = lane; q < len; q += 32) pq[rs + q] = (static_cast<uint32_t>(p) << 16) | static_cast<uint32_t>(q);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {  // entry c lies in the last row whose start is <= c
+    int lo = 0, hi = kq - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (rowstart[mid] <= c) lo = mid; else hi = mid - 1;
+    }
+    pq[c] = (static_cast<uint32_t>(lo) << 16) | static_cast<uint32_t>(c - rowstart[lo]);
   }
   __syncthreads();
 
@@ -306,9 +309,11 @@ __device__ __forceinline__ void bitonic_desc_regs(K (&a)[E], int lane) {
   }
 }
 
+constexpr int kTieCap = 256;  // entries of the per-warp list of candidates that tie with tau
+
 struct RouterRegLayout {
   int cta_bytes, warp_bytes;
-  int off_sorted, off_ids, off_win, off_cs;
+  int off_sorted, off_ids, off_win, off_cs, off_tl;
   int nkp, kp, kq, C, Cp;
 };
 
@@ -345,10 +350,13 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     }
   }
   __syncthreads();
-  for (int p = warp; p < kq; p += nwarps) {
-    const int len = min(k / (p + 1), kq);
-    const int rs = rowstart[p];
-    for (int q = lane; q < len; q += 32) pq[rs + q] = (static_cast<uint32_t>(p) << 16) | static_cast<uint32_t>(q);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {  // entry c lies in the last row whose start is <= c
+    int lo = 0, hi = kq - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (rowstart[mid] <= c) lo = mid; else hi = mid - 1;
+    }
+    pq[c] = (static_cast<uint32_t>(lo) << 16) | static_cast<uint32_t>(c - rowstart[lo]);
   }
   __syncthreads();
 
@@ -361,6 +369,8 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
   uint16_t* ib = ia + nkp;
   uint64_t* win = reinterpret_cast<uint64_t*>(wbase + L.off_win);
   uint32_t* cs = reinterpret_cast<uint32_t*>(wbase + L.off_cs);
+  uint32_t* tl = reinterpret_cast<uint32_t*>(wbase + L.off_tl);  // flat ids of candidates equal to tau
+  int* tcnt = reinterpret_cast<int*>(tl + kTieCap);
   constexpr int LOW = OrdLowBits<T>::value;
   int nsteps = 0;  // binary-search steps covering [0, nk]
   while ((1 << nsteps) <= nk) ++nsteps;
@@ -461,23 +471,101 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       if (LOW > 0 && (tau >> 31) == 0) tau |= (1u << LOW) - 1u;
     }
 
-    int filled = 0;
+    // emit everything above tau; collect the staircase candidates equal to tau in the tie list
+    int filled = 0, nties = 0;
     for (int base = 0; base < C; base += 32) {
       const int c = base + lane;
-      const bool g = (c < C) && (cs[c] > tau);
+      const uint32_t v = (c < C) ? cs[c] : 0u;
+      const bool g = (c < C) && (v > tau);
+      const bool eq = (c < C) && (v == tau);
       const unsigned bal = __ballot_sync(kFull, g);
-      if (g) {
-        const int pos = filled + __popc(bal & ((1u << lane) - 1u));
+      const unsigned beq = __ballot_sync(kFull, eq);
+      if (g || eq) {
         const uint32_t e = pq[c];
         const uint32_t flat = static_cast<uint32_t>(ia[e >> 16]) * static_cast<uint32_t>(nk) + ib[e & 0xFFFFu];
-        if (pos < k) win[pos] = make_key(cs[c], flat);
+        if (g) {
+          const int pos = filled + __popc(bal & ((1u << lane) - 1u));
+          if (pos < k) win[pos] = make_key(v, flat);
+        } else {
+          const int pos = nties + __popc(beq & ((1u << lane) - 1u));
+          if (pos < kTieCap) tl[pos] = flat;
+        }
       }
       filled += __popc(bal);
+      nties += __popc(beq);
     }
     int need = k - filled;
 
-    // 4. ties with tau: row i = r*32 + lane ties with sorted-b positions [gt, ge); the E rows of a
-    //    lane are searched in lock step so their shared-memory loads overlap
+    // 4. the remaining `need` slots go to the candidates equal to tau with the lowest flat ids.
+    //    Outside the staircase every score is <= tau, and along a row (fixed rank p of the first
+    //    half) the scores do not increase, so the ties outside the staircase are the runs that
+    //    continue a row past its last staircase cell, plus runs from q = 0 in the rows below the
+    //    staircase.  They are gathered in rank space into the tie list; if the list overflows, the
+    //    exhaustive per-row search below takes over.
+    if (lane == 0) *tcnt = nties;
+    __syncwarp();
+    for (int p = lane; p < kq; p += 32) {
+      const int len = min(k / (p + 1), kq);
+      if (len < nk && cs[rowstart[p] + len - 1] >= tau) {
+        const float a = sa[p];
+        const uint32_t ida = static_cast<uint32_t>(ia[p]) * static_cast<uint32_t>(nk);
+        for (int q = len; q < nk; ++q) {
+          if (f32_to_ord(round_to<T>(__fadd_rn(a, sb[q])) + 0.0f) != tau) break;
+          const int pos = atomicAdd(tcnt, 1);
+          if (pos < kTieCap) tl[pos] = ida + ib[q];
+        }
+      }
+    }
+    {
+      const float b0 = sb[0];
+      for (int base = kq; base < nk; base += 32) {  // rows below the staircase: tie runs start at q = 0
+        const int p = base + lane;
+        const bool hit = (p < nk) && (f32_to_ord(round_to<T>(__fadd_rn(sa[p < nk ? p : 0], b0)) + 0.0f) == tau);
+        if (hit) {
+          const float a = sa[p];
+          const uint32_t ida = static_cast<uint32_t>(ia[p]) * static_cast<uint32_t>(nk);
+          for (int q = 0; q < nk; ++q) {
+            if (f32_to_ord(round_to<T>(__fadd_rn(a, sb[q])) + 0.0f) != tau) break;
+            const int pos = atomicAdd(tcnt, 1);
+            if (pos < kTieCap) tl[pos] = ida + ib[q];
+          }
+        }
+        if (__ballot_sync(kFull, hit) == 0u) break;  // the rows are sorted: no later row can tie
+      }
+    }
+    __syncwarp();
+    nties = *tcnt;
+    __syncwarp();
+    const bool tie_list_ok = nties <= kTieCap;
+    if (tie_list_ok && need > 0) {
+      uint32_t phi = 0xFFFFFFFFu;  // ids <= phi are taken
+      if (nties > need) {
+        // phi = the need-th smallest id = the largest v with fewer than `need` ids below v
+        uint32_t v = 0;
+        const int topbit = 31 - __clz(static_cast<unsigned>(nk) * static_cast<unsigned>(nk));
+        for (int bit = topbit; bit >= 0; --bit) {
+          const uint32_t trial = v | (1u << bit);
+          int below = 0;
+          for (int i = lane; i < nties; i += 32) below += (tl[i] < trial) ? 1 : 0;
+          below = __reduce_add_sync(kFull, below);
+          if (below < need) v = trial;
+        }
+        phi = v;
+      }
+      for (int base = 0; base < nties; base += 32) {
+        const int i = base + lane;
+        const uint32_t id = (i < nties) ? tl[i] : 0xFFFFFFFFu;
+        const bool take = (i < nties) && (id <= phi);
+        const unsigned bal = __ballot_sync(kFull, take);
+        if (take) win[filled + __popc(bal & ((1u << lane) - 1u))] = make_key(tau, id);
+        filled += __popc(bal);
+      }
+      need = k - filled;
+    }
+
+    // 4b. overflow path (more than kTieCap ties, e.g. constant inputs): row i = r*32 + lane ties with
+    //     sorted-b positions [gt, ge); rows are then visited in index order
+    if (!tie_list_ok) {
     int lo_ge[E], hi_ge[E], lo_gt[E], hi_gt[E];
     float arow[E];
 #pragma unroll
@@ -523,11 +611,27 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
         }
       }
     }
+    }  // overflow path
     for (int r = filled + lane; r < kp; r += 32) win[r] = 0;
     __syncwarp();
 
     // 5. order the winners (registers when they fit, shared memory otherwise) and write out
-    if (kp <= 32) {
+    if (sizeof(T) == 2 && kp == 64 && nk <= 256) {
+      // 16-bit scores and 16-bit flat ids: sort 32-bit keys
+      uint32_t w[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint64_t key = win[r * 32 + lane];
+        w[r] = key == 0 ? 0u : static_cast<uint32_t>(HalfKey<T>::make(key_val(key), key_id(key)));
+      }
+      bitonic_desc_regs<2, uint32_t>(w, lane);
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint32_t key32 = w[r];
+        const float sc = static_cast<float>(HalfKey<T>::value(static_cast<typename HalfKey<T>::type>(key32)));
+        win[r * 32 + lane] = make_key(f32_to_ord(sc + 0.0f), HalfKey<T>::id(static_cast<typename HalfKey<T>::type>(key32)));
+      }
+    } else if (kp <= 32) {
       uint64_t w[1] = {lane < kp ? win[lane] : 0};
       bitonic_desc_regs<1, uint64_t>(w, lane);
       if (lane < kp) win[lane] = w[0];
@@ -588,6 +692,8 @@ RouterRegLayout make_reg_layout(int nk, int k) {
   off += (L.kp < 32 ? 32 : L.kp) * 8;
   L.off_cs = off;
   off += L.Cp * 4;
+  L.off_tl = off;
+  off += (kTieCap + 4) * 4;
   L.warp_bytes = static_cast<int>(align_up(off, 16));
   return L;
 }

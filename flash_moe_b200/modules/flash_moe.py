@@ -115,11 +115,11 @@ class FlashMoE(nn.Module):
         return ws
 
     def kernels_per_forward(self) -> int:
-        """Kernels of this library launched by one forward (16-bit dtypes): batch-norm finalize + apply,
-        router GEMM (log-softmax fused for num_keys <= 256), top-k, experts (2 kernels when the tables
-        fit L2 and are gathered per token, 5 with the expert-centric sort), MLP up GEMM, MLP down GEMM."""
-        n = 2 + 1 + 1 + 1 + 1
-        if self.num_keys > 256:
+        """Kernels of this library launched by one forward (16-bit dtypes): batch-norm apply, router GEMM,
+        top-k (with the log-softmax inside for num_keys <= 1024), experts (2 kernels when the tables fit L2
+        and are gathered per token, 5 with the expert-centric sort), MLP up GEMM, MLP down GEMM."""
+        n = 1 + 1 + 1 + 1 + 1
+        if self.num_keys > 1024:
             n += 1  # separate log-softmax pass
         table_bytes = 2 * self.num_experts * self.hidden_size * self.down_embed.weight.element_size()
         if self.down_embed.weight.element_size() == 2 and table_bytes <= 96 * 1024 * 1024:
@@ -129,7 +129,7 @@ class FlashMoE(nn.Module):
             if (self.num_experts + 2047) // 2048 > 16:
                 n += 1  # two-level scan
         if self.training:
-            n += 1  # batch statistics pass
+            n += 2  # batch statistics pass + finalize
         return n
 
     def forward(
