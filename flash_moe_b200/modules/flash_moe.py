@@ -65,7 +65,7 @@ class StageTimer:
 
 
 class FlashMoE(nn.Module):
-    def __init__(self, config: FlashMoEConfig, overlap_shared_mlp: bool = True):
+    def __init__(self, config: FlashMoEConfig, overlap_shared_mlp: bool = False):
         super().__init__()
         self.hidden_size = config.hidden_size
         self.intermediate_size = config.intermediate_size
