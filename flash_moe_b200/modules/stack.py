@@ -1,0 +1,34 @@
+"""A residual stack of FlashMoE layers used as the MLP path of a decoder: x <- x + layer(x).
+
+The reference ships the single layer only; this is the caller-side composition BASELINE's
+multi-layer configuration describes (layer l seeded with torch.manual_seed(l))."""
+
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.nn as nn
+
+from .flash_moe import FlashMoE, FlashMoEConfig
+
+
+class FlashMoEStack(nn.Module):
+    def __init__(self, config: FlashMoEConfig, num_layers: int, seeds=None):
+        super().__init__()
+        layers = []
+        for i in range(num_layers):
+            if seeds is not None:
+                torch.manual_seed(seeds[i])
+            layers.append(FlashMoE(config))
+        self.layers = nn.ModuleList(layers)
+
+    def forward(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, List[torch.Tensor]]:
+        """Returns the final hidden states and every layer's router logits."""
+        all_logits = []
+        x = hidden_states
+        for layer in self.layers:
+            y, logits = layer(x)
+            x = x + y
+            all_logits.append(logits)
+        return x, all_logits
