@@ -6,7 +6,7 @@ public interface: `FlashMoE` / `FlashMoEConfig` and the three op entry points.
 """
 
 from ._lib import FmoeError, check_status, read_status  # noqa: F401
-from .modules.flash_moe import FlashMoE, FlashMoEConfig, StageTimer  # noqa: F401
+from .modules.flash_moe import FlashMoE, FlashMoEConfig, GraphedFlashMoE, StageTimer  # noqa: F401
 from .ops.flash_expert import flash_expert_func, triton_flash_expert_func  # noqa: F401
 from .ops.flash_mlp import flash_mlp_func, triton_flash_mlp_func  # noqa: F401
 from .ops.flash_router import flash_router_func, triton_flash_router_func  # noqa: F401

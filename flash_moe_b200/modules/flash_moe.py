@@ -208,3 +208,34 @@ class FlashMoE(nn.Module):
             self.last_indices, self.last_gates = idx, gates
         router_logits = logits.view(T, 2, nk).transpose(0, 1)
         return y.view(bsz, seq_len, H), router_logits
+
+
+class GraphedFlashMoE:
+    """One layer forward captured in a CUDA graph for a fixed input shape: the seven kernels replay
+    back to back without per-launch host work.  Write the input into ``static_input`` (or pass it to
+    ``__call__``, which copies it there), then read ``static_output`` / ``static_router_logits``; they
+    are overwritten by the next replay."""
+
+    def __init__(self, layer: FlashMoE, example: torch.Tensor, warmup: int = 3):
+        if layer.training:
+            raise _lib.FmoeError("capture the layer in eval mode (train mode updates host-side counters)")
+        self.layer = layer
+        self.static_input = example.clone()
+        side = torch.cuda.Stream(device=example.device)
+        side.wait_stream(torch.cuda.current_stream(example.device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):
+                layer(self.static_input)
+        torch.cuda.current_stream(example.device).wait_stream(side)
+        torch.cuda.synchronize(example.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.static_output, self.static_router_logits = layer(self.static_input)
+
+    def replay(self) -> None:
+        self.graph.replay()
+
+    def __call__(self, hidden_states: torch.Tensor):
+        self.static_input.copy_(hidden_states)
+        self.graph.replay()
+        return self.static_output, self.static_router_logits

@@ -131,3 +131,22 @@ def test_state_dict_and_forward_only_contract():
     assert torch.equal(ours(x)[0], other(x)[0])
     with pytest.raises(Exception):
         ours(x.cpu())
+
+
+def test_cuda_graph_replay_matches_eager():
+    from flash_moe_b200 import GraphedFlashMoE, check_status
+
+    ref, ours = make_layer_pair(256, 512, 1024, 8, True, torch.bfloat16)
+    ours.eval()
+    x = randn((2, 96, 256), 4, torch.bfloat16).cuda()
+    with torch.no_grad():
+        y, logits = ours(x)
+        g = GraphedFlashMoE(ours, x)
+        y2, logits2 = (t.clone() for t in g(x))  # the static outputs are overwritten by the next replay
+        x3 = randn((2, 96, 256), 5, torch.bfloat16).cuda()
+        y3, _ = g(x3)
+        want3, _ = ours(x3)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(y, y2) and torch.equal(logits, logits2)
+    assert torch.equal(y3, want3)
