@@ -89,6 +89,7 @@ size_t mlp_ws(int64_t T, int I, int dtype) { return align_up(static_cast<size_t>
 int mlp_up(const void* x, const void* gw, const void* uw, void* h, int dtype, int64_t T, int H, int I, int32_t* status,
            cudaStream_t stream) {
   const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(x) && aligned16(gw) && aligned16(uw);
+  if (tc && gemm_pair_supported(T, I, H)) return launch_gemm_swiglu_pair(x, gw, uw, h, dtype, T, I, H, status, stream);
   if (tc) return launch_gemm_swiglu(x, gw, uw, h, dtype, T, I, H, status, stream);
   return launch_simt_gemm(x, H, gw, uw, nullptr, h, I, dtype, 1, T, I, H, stream);
 }
@@ -97,6 +98,7 @@ int mlp_down(const void* h, const void* dw, const float* addend, void* out, int 
              int32_t* status, cudaStream_t stream) {
   const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(dw) && aligned16(out) &&
                   (addend == nullptr || aligned16(addend));
+  if (tc && gemm_pair_supported(T, H, I)) return launch_gemm_add_pair(h, dw, addend, out, dtype, T, H, I, status, stream);
   if (tc) return launch_gemm_add(h, dw, addend, out, dtype, T, H, I, status, stream);
   return launch_simt_gemm(h, I, dw, nullptr, addend, out, H, dtype, 0, T, H, I, stream);
 }

@@ -126,6 +126,12 @@ int launch_gemm_add(const void* a, const void* b, const float* addend, void* out
 int launch_gemm_router(const void* xn, int64_t a_cols, int a_half_koff, const void* w, void* logits, void* log_probs,
                        int dtype, int64_t M, int nk, int K, int32_t* status, cudaStream_t stream);
 bool gemm_router_fused_supported(int nk);
+// CTA-pair (cta_group::2) versions of the two shared-MLP GEMMs (gemm_sm100_pair.cu)
+bool gemm_pair_supported(int64_t M, int N, int K);
+int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I,
+                            int K, int32_t* status, cudaStream_t stream);
+int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N,
+                         int K, int32_t* status, cudaStream_t stream);
 
 // fp32-FMA GEMM on CUDA cores (simt_gemm.cu): float32 modules and shapes TMA cannot address.
 int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1, const float* addend, void* out,
