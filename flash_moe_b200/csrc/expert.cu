@@ -243,23 +243,27 @@ template <> struct Mma16816<__half> {
   }
 };
 
-// One warp per (token, group of 16 of its experts); the four warps of a CTA take consecutive
-// groups, so the groups of one token share its x row through L1.  Loads are issued in batches of
-// four 32-column blocks (12 x 16 B per lane in flight) to cover the L2 latency of the gather.
-template <typename T>
+// One warp per (token, group of 16 of its experts).  The token's x row is parked in the warp's
+// slice of shared memory (read back as B fragments right before each MMA), so every register that
+// waits for data waits for a gathered down row: batches of UNROLL 32-column blocks keep
+// 2 * UNROLL x 16 B per lane in flight to cover the L2 latency of the gather.
+template <typename T, int UNROLL>
 __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restrict__ x, const T* __restrict__ down,
                                                                const int64_t* __restrict__ idx,
                                                                const T* __restrict__ gates, float* __restrict__ gs,
-                                                               int64_t ntok, int H, int64_t N, int k,
+                                                               int64_t ntok, int H, int64_t N, int k, int xs_stride,
                                                                int32_t* status) {
-  constexpr int UNROLL = 4;
+  extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
+  uint4* xs = xs_all + (threadIdx.x >> 5) * xs_stride;  // xs_stride uint4 per warp, >= ceil(H/256)*32
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int groups = (k + 15) >> 4;
   const int64_t tasks = ntok * groups;
+  const int hv = H >> 3;  // 16-byte pieces per row
   bool bad = false;
+  int64_t t_in_smem = -1;
   for (int64_t task = warp_global; task < tasks; task += warps_total) {
     const int64_t t = task / groups;
     const int G = static_cast<int>(task - t * groups);
@@ -272,22 +276,29 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
     if ((ja < k && !oka) || (jb < k && !okb)) bad = true;
     const T* ra = down + (oka ? ea : 0) * H + 8 * tq;
     const T* rb = down + (okb ? eb : 0) * H + 8 * tq;
-    const T* rx = x + t * H + 8 * tq;
+    if (t != t_in_smem) {  // warp-uniform
+      __syncwarp();
+      const T* xr = x + t * H;
+      for (int c = lane; c < xs_stride; c += 32) xs[c] = (c < hv) ? ldg16(xr + c * 8) : make_uint4(0, 0, 0, 0);
+      __syncwarp();
+      t_in_smem = t;
+    }
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c0 = 0; c0 < H; c0 += 32 * UNROLL) {
-      uint4 xq[UNROLL], qa[UNROLL], qb[UNROLL];
+      uint4 qa[UNROLL], qb[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int col = c0 + 32 * u;
         const bool in = col + 8 * tq < H;
-        xq[u] = in ? ldg16(rx + col) : make_uint4(0, 0, 0, 0);
         qa[u] = in ? ldg16(ra + col) : make_uint4(0, 0, 0, 0);
         qb[u] = in ? ldg16(rb + col) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
-        Mma16816<T>::run(c, qa[u].x, qb[u].x, qa[u].y, qb[u].y, xq[u].x, xq[u].y);
-        Mma16816<T>::run(c, qa[u].z, qb[u].z, qa[u].w, qb[u].w, xq[u].z, xq[u].w);
+        const int piece = ((c0 + 32 * u) >> 3) + tq;
+        const uint4 xq = piece < xs_stride ? xs[piece] : make_uint4(0, 0, 0, 0);
+        Mma16816<T>::run(c, qa[u].x, qb[u].x, qa[u].y, qb[u].y, xq.x, xq.y);
+        Mma16816<T>::run(c, qa[u].z, qb[u].z, qa[u].w, qb[u].w, xq.z, xq.w);
       }
     }
     if (tq == 0) {
@@ -468,8 +479,12 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
       const int64_t want = (T_ * ((k + 15) / 16) + 3) / 4;
       const int64_t cap = static_cast<int64_t>(sms) * 16;
       const int grid = static_cast<int>(want < cap ? want : cap);
-      expert_scores_mma_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down), idx,
-                                                           static_cast<const T*>(gates), w.gs, T_, H, N, k, status);
+      const int xs_stride = ((H + 255) / 256) * 32;  // uint4 per warp, rows padded to 256 columns
+      const int smem = 4 * xs_stride * 16;
+      auto kern = expert_scores_mma_kernel<T, 8>;
+      if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down), idx,
+                                        static_cast<const T*>(gates), w.gs, T_, H, N, k, xs_stride, status);
       FMOE_LAUNCH_CHECK();
     }
   } else {
