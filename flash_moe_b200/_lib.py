@@ -59,6 +59,8 @@ class LayerArgs(ctypes.Structure):
         ("norm_topk_prob", ctypes.c_int32),
         ("bn_momentum", ctypes.c_float),
         ("bn_eps", ctypes.c_float),
+        ("bn_global_sums", ctypes.c_void_p),
+        ("bn_global_count", ctypes.c_int64),
     ]
 
 
@@ -75,6 +77,8 @@ SIGNATURES = {
     "fmoe_router_topk": (_I, [_P, _I, _L, _I, _I, _P, _P, _P, _I, _P]),
     "fmoe_router_front_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fmoe_router_front": (_I, [_P, _P, _P, _P, _I, _F, _F, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
+    "fmoe_bn_batch_sums_workspace_bytes": (_Z, [_I]),
+    "fmoe_bn_batch_sums": (_I, [_P, _I, _L, _I, _P, _P, _Z, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_expert_static_scratch_bytes": (_Z, []),

@@ -6,7 +6,9 @@ namespace fmoe {
 
 size_t bn_workspace_bytes(int H);
 int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, int training, float momentum, float eps,
-              int dtype, int64_t ntok, int H, float* ws, cudaStream_t stream);
+              int dtype, int64_t ntok, int H, float* ws, const float* global_sums, int64_t global_count,
+              cudaStream_t stream);
+int launch_bn_sums(const void* x, int dtype, int64_t ntok, int H, float* ws, float* sums, cudaStream_t stream);
 
 int device_sm_count() {
   static int cache[64] = {0};
@@ -61,7 +63,7 @@ size_t router_front_ws(int64_t T, int H, int dtype) {
 // logp == nullptr: stop after the logits (the caller applies the log-softmax elsewhere)
 int router_front(const void* x, const void* w, void* rm, void* rv, int training, float momentum, float eps,
                  void* logits, void* logp, int dtype, int64_t T, int H, int nk, void* ws, size_t ws_bytes,
-                 int32_t* status, cudaStream_t stream) {
+                 int32_t* status, cudaStream_t stream, const float* bn_sums = nullptr, int64_t bn_count = 0) {
   if (!valid_dtype(dtype) || T < 0 || H <= 0 || nk <= 0) return FMOE_ERR_BAD_ARG;
   if (T == 0) return FMOE_OK;
   if (x == nullptr || w == nullptr || logits == nullptr) return FMOE_ERR_BAD_ARG;
@@ -69,7 +71,7 @@ int router_front(const void* x, const void* w, void* rm, void* rv, int training,
   Carver c(ws);
   void* xn = c.take(static_cast<size_t>(T) * H * dtype_size(dtype));
   float* bnws = static_cast<float*>(c.take(bn_workspace_bytes(H)));
-  int rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, stream);
+  int rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, bn_sums, bn_count, stream);
   if (rc != FMOE_OK) return rc;
   const bool tc = is16(dtype) && (H % 8 == 0) && aligned16(w);
   if (logp != nullptr && tc && gemm_router_fused_supported(nk) && aligned16(logits) && aligned16(logp))
@@ -169,6 +171,16 @@ int fmoe_router_front(const void* x, const void* router_weight, void* running_me
                       static_cast<cudaStream_t>(stream));
 }
 
+size_t fmoe_bn_batch_sums_workspace_bytes(int hidden) { return hidden > 0 ? bn_workspace_bytes(hidden) : 0; }
+
+int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden, float* sums, void* workspace,
+                       size_t workspace_bytes, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype) || hidden <= 0 || num_tokens <= 0) return FMOE_ERR_BAD_ARG;
+  if (workspace == nullptr || workspace_bytes < bn_workspace_bytes(hidden)) return FMOE_ERR_WORKSPACE;
+  return launch_bn_sums(x, dtype, num_tokens, hidden, static_cast<float*>(workspace), sums,
+                        static_cast<cudaStream_t>(stream));
+}
+
 size_t fmoe_expert_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k) {
   return expert_workspace_bytes(num_tokens, hidden, num_experts, top_k);
 }
@@ -244,7 +256,7 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 0, s);
   rc = router_front(a->x, a->router_gate, a->running_mean, a->running_var, a->training, a->bn_momentum, a->bn_eps,
                     a->router_logits, topk_from_logits ? nullptr : w.logp, dtype, T, H, nk, w.front, w.front_bytes,
-                    a->status, s);
+                    a->status, s, a->training ? a->bn_global_sums : nullptr, a->bn_global_count);
   if (rc != FMOE_OK) return rc;
   FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
 

@@ -34,15 +34,21 @@ __global__ void bn_partial_kernel(const T* __restrict__ x, int64_t ntok, int H, 
 template <typename T>
 __global__ void bn_finalize_kernel(const float* __restrict__ psum, const float* __restrict__ psq, T* running_mean,
                                    T* running_var, int training, float momentum, float eps, int64_t ntok, int H,
-                                   float* __restrict__ mean_out, float* __restrict__ invstd_out) {
+                                   float* __restrict__ mean_out, float* __restrict__ invstd_out,
+                                   const float* __restrict__ global_sums) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   float mean, var;
   if (training) {
     double s = 0.0, q = 0.0;
-    for (int i = 0; i < kBnSplits; ++i) {
-      s += static_cast<double>(psum[static_cast<int64_t>(i) * H + c]);
-      q += static_cast<double>(psq[static_cast<int64_t>(i) * H + c]);
+    if (global_sums != nullptr) {  // sums over ALL shards' rows (ntok is then the global row count)
+      s = static_cast<double>(global_sums[c]);
+      q = static_cast<double>(global_sums[H + c]);
+    } else {
+      for (int i = 0; i < kBnSplits; ++i) {
+        s += static_cast<double>(psum[static_cast<int64_t>(i) * H + c]);
+        q += static_cast<double>(psq[static_cast<int64_t>(i) * H + c]);
+      }
     }
     const double m = s / static_cast<double>(ntok);
     double v = q / static_cast<double>(ntok) - m * m;
@@ -62,6 +68,20 @@ __global__ void bn_finalize_kernel(const float* __restrict__ psum, const float* 
   }
   mean_out[c] = mean;
   invstd_out[c] = 1.0f / sqrtf(var + eps);
+}
+
+// sums[c] = sum_r x[r][c], sums[H + c] = sum_r x[r][c]^2 from the split partials (for the cross-rank all-reduce)
+__global__ void bn_sums_kernel(const float* __restrict__ psum, const float* __restrict__ psq, int H,
+                               float* __restrict__ sums) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  double s = 0.0, q = 0.0;
+  for (int i = 0; i < kBnSplits; ++i) {
+    s += static_cast<double>(psum[static_cast<int64_t>(i) * H + c]);
+    q += static_cast<double>(psq[static_cast<int64_t>(i) * H + c]);
+  }
+  sums[c] = static_cast<float>(s);
+  sums[H + c] = static_cast<float>(q);
 }
 
 // blockIdx.x / threadIdx.x pick a fixed group of VEC columns (mean / inv-std stay in registers),
@@ -132,19 +152,20 @@ __global__ void log_softmax_halves_kernel(const T* __restrict__ logits, T* __res
 
 template <typename T>
 int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float momentum, float eps, int64_t ntok, int H,
-             float* ws, cudaStream_t stream) {
+             float* ws, const float* global_sums, int64_t global_count, cudaStream_t stream) {
   float* psum = ws;
   float* psq = ws + static_cast<size_t>(kBnSplits) * H;
   float* mean = psq + static_cast<size_t>(kBnSplits) * H;
   float* invstd = mean + H;
-  if (training) {
+  if (training && global_sums == nullptr) {
     dim3 grid((H + 127) / 128, kBnSplits);
     bn_partial_kernel<T><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), ntok, H, psum, psq);
     FMOE_LAUNCH_CHECK();
   }
   if (training) {
-    bn_finalize_kernel<T><<<(H + 127) / 128, 128, 0, stream>>>(psum, psq, static_cast<T*>(rm), static_cast<T*>(rv),
-                                                              training, momentum, eps, ntok, H, mean, invstd);
+    bn_finalize_kernel<T><<<(H + 127) / 128, 128, 0, stream>>>(
+        psum, psq, static_cast<T*>(rm), static_cast<T*>(rv), training, momentum, eps,
+        global_sums != nullptr ? global_count : ntok, H, mean, invstd, global_sums);
     FMOE_LAUNCH_CHECK();
   }
   constexpr int VEC = Vec16<T>::N;
@@ -165,15 +186,34 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
 
 size_t bn_workspace_bytes(int H) { return static_cast<size_t>(2 * kBnSplits + 2) * H * sizeof(float); }
 
+// per-feature sum and sum of squares of this rank's rows: sums[0:H], sums[H:2H] (float32)
+int launch_bn_sums(const void* x, int dtype, int64_t ntok, int H, float* ws, float* sums, cudaStream_t stream) {
+  if (x == nullptr || ws == nullptr || sums == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
+  float* psum = ws;
+  float* psq = ws + static_cast<size_t>(kBnSplits) * H;
+  dim3 grid((H + 127) / 128, kBnSplits);
+  switch (dtype) {
+    case FMOE_DTYPE_F32: bn_partial_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), ntok, H, psum, psq); break;
+    case FMOE_DTYPE_BF16: bn_partial_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ntok, H, psum, psq); break;
+    case FMOE_DTYPE_F16: bn_partial_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), ntok, H, psum, psq); break;
+    default: return FMOE_ERR_BAD_ARG;
+  }
+  FMOE_LAUNCH_CHECK();
+  bn_sums_kernel<<<(H + 127) / 128, 128, 0, stream>>>(psum, psq, H, sums);
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
 int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, int training, float momentum, float eps,
-              int dtype, int64_t ntok, int H, float* ws, cudaStream_t stream) {
+              int dtype, int64_t ntok, int H, float* ws, const float* global_sums, int64_t global_count,
+              cudaStream_t stream) {
   if (x == nullptr || xn == nullptr || ws == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
   if (!training && (running_mean == nullptr || running_var == nullptr)) return FMOE_ERR_BAD_ARG;
   if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(x) || !aligned16(xn)) return FMOE_ERR_ALIGNMENT;
   switch (dtype) {
-    case FMOE_DTYPE_F32: return bn_typed<float>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
-    case FMOE_DTYPE_BF16: return bn_typed<__nv_bfloat16>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
-    case FMOE_DTYPE_F16: return bn_typed<__half>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, stream);
+    case FMOE_DTYPE_F32: return bn_typed<float>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, global_sums, global_count, stream);
+    case FMOE_DTYPE_BF16: return bn_typed<__nv_bfloat16>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, global_sums, global_count, stream);
+    case FMOE_DTYPE_F16: return bn_typed<__half>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, global_sums, global_count, stream);
     default: return FMOE_ERR_BAD_ARG;
   }
 }

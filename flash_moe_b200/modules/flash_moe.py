@@ -137,9 +137,14 @@ class FlashMoE(nn.Module):
         hidden_states: torch.Tensor,
         return_routing: bool = False,
         stage_timer: Optional[StageTimer] = None,
+        bn_sync_group=None,
         **kwargs,
     ) -> Tuple[torch.Tensor, torch.Tensor]:
         """(y[B,S,H], router_logits[2, B*S, num_keys]) like the reference; forward only.
+
+        ``bn_sync_group``: a torch.distributed process group over which the tokens are sharded.  In
+        training mode the router batch-norm then uses the statistics of the whole (global) batch: the
+        ranks all-reduce 2*H float32 sums before the router GEMM.
 
         ``return_routing=True`` additionally keeps the selected expert ids and gates in
         ``self.last_indices`` / ``self.last_gates``.
@@ -167,6 +172,21 @@ class FlashMoE(nn.Module):
         code = _lib.dtype_code(x)
         ws_bytes = L.fmoe_layer_workspace_bytes(T, H, I, N, nk, k, code)
         ws = self._workspace(dev, ws_bytes)
+
+        bn_sums, bn_count = None, 0
+        if training and bn_sync_group is not None:
+            import torch.distributed as dist
+
+            bn_sums = torch.empty(2 * H, dtype=torch.float32, device=dev)
+            bws_bytes = L.fmoe_bn_batch_sums_workspace_bytes(H)
+            bws = torch.empty(bws_bytes, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                _lib.check(L.fmoe_bn_batch_sums(x.data_ptr(), code, T, H, bn_sums.data_ptr(), bws.data_ptr(), bws_bytes,
+                                                _lib.current_stream_ptr(dev)), "fmoe_bn_batch_sums")
+            count = torch.tensor([float(T)], dtype=torch.float64, device=dev)
+            dist.all_reduce(bn_sums, group=bn_sync_group)
+            dist.all_reduce(count, group=bn_sync_group)
+            bn_count = int(count.item())
 
         with torch.cuda.device(dev):
             main = torch.cuda.current_stream(dev)
@@ -198,6 +218,8 @@ class FlashMoE(nn.Module):
             a.norm_topk_prob = int(bool(self.norm_topk_prob))
             a.bn_momentum = momentum
             a.bn_eps = float(bn.eps)
+            a.bn_global_sums = _lib.ptr(bn_sums)
+            a.bn_global_count = bn_count
             rc = L.fmoe_layer_forward(ctypes.byref(a))
         _lib.check(rc, "fmoe_layer_forward")
         # The side stream is joined back into the calling stream inside the library call, so the

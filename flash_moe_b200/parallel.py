@@ -68,7 +68,7 @@ class ExpertShardedExperts:
     """Fine-grained experts with the tables sharded over the ranks of `group` (see module docstring).
 
     `expert_fn(x, down, up, indices, gates) -> float32 [rows, H]` evaluates local experts; the default is
-    the CUDA op of this package.  Tests on CPU pass the oracle.
+    the CUDA op of this package; CPU tests pass a stand-in with the same signature.
     """
 
     def __init__(self, down_shard: torch.Tensor, up_shard: torch.Tensor, num_experts: int, group=None,

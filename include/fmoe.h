@@ -80,6 +80,17 @@ int fmoe_router_front(const void* x, const void* router_weight, void* running_me
                       fmoe_stream_t stream);
 
 /*
+ * Per-feature batch statistics of this rank's rows for the router batch-norm under token sharding:
+ * sums[0:H] = sum_r x[r, c], sums[H:2H] = sum_r x[r, c]^2 (float32).  The ranks all-reduce these 2*H
+ * floats and hand the result to fmoe_layer_forward (bn_global_sums / bn_global_count), which then
+ * normalises with the statistics of the WHOLE batch like the unsharded nn.BatchNorm1d in training
+ * mode does (flash_moe/modules/flash_moe.py:49,:65).
+ */
+size_t fmoe_bn_batch_sums_workspace_bytes(int hidden);
+int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden, float* sums, void* workspace,
+                       size_t workspace_bytes, fmoe_stream_t stream);
+
+/*
  * Fine-grained experts: out[t] = sum_j silu(<x[t], down[idx[t,j]]>) * gates[t,j] * up[idx[t,j]].
  * Replaces triton_flash_expert_func(hidden_states, down_weights, up_weights, indices, routing_weights)
  *   flash_moe/ops/triton/flash_expert.py:831-836 (forward :580-649, preprocessing :528-577,
@@ -172,6 +183,8 @@ typedef struct fmoe_layer_args {
   int32_t norm_topk_prob;
   float bn_momentum;
   float bn_eps;
+  const float* bn_global_sums; /* nullable; training only: [2*H] sums over all shards (fmoe_bn_batch_sums) */
+  int64_t bn_global_count;     /* rows behind bn_global_sums */
 } fmoe_layer_args;
 
 size_t fmoe_layer_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int64_t num_experts, int num_keys,

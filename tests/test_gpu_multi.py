@@ -33,6 +33,19 @@ WORKER = textwrap.dedent(
         s, e = token_shard(300, rank, world)
         part, _ = layer(x[:, s:e].contiguous())
     assert torch.equal(part, full[:, s:e]), "token shard differs from the unsharded forward"
+    # --- training mode: batch-norm statistics of the WHOLE batch under token sharding
+    torch.manual_seed(0)
+    tl_full = FlashMoE(FlashMoEConfig(256, 512, "silu", 1024, 8)).to(dev).train()
+    torch.manual_seed(0)
+    tl_shard = FlashMoE(FlashMoEConfig(256, 512, "silu", 1024, 8)).to(dev).train()
+    xf = (torch.randn(1, 300, 256, generator=torch.Generator().manual_seed(2)) * 1.7 + 0.4).to(dev)
+    with torch.no_grad():
+        _, logits_full = tl_full(xf)
+        s, e = token_shard(300, rank, world)
+        _, logits_part = tl_shard(xf[:, s:e].contiguous(), bn_sync_group=dist.group.WORLD)
+    torch.testing.assert_close(logits_part, logits_full[:, s:e], rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(tl_shard.router_norm.running_mean, tl_full.router_norm.running_mean, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(tl_shard.router_norm.running_var, tl_full.router_norm.running_var, rtol=1e-5, atol=1e-6)
     # --- experts sharded by id % world, all-to-all dispatch / combine
     g = torch.Generator().manual_seed(3)
     T, H, N, k = 512, 256, 4096, 8
