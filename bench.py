@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the FlashMoE layer forward (BASELINE config 2) on 1..N B200s.
+"""Benchmark of the FlashMoE layer forward (benchmark configuration 2: the reference's quick-start shape) on 1..N B200s.
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \

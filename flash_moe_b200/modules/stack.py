@@ -1,7 +1,7 @@
 """A residual stack of FlashMoE layers used as the MLP path of a decoder: x <- x + layer(x).
 
-The reference ships the single layer only; this is the caller-side composition BASELINE's
-multi-layer configuration describes (layer l seeded with torch.manual_seed(l))."""
+The reference ships the single layer only; this is the caller-side composition of the
+multi-layer benchmark configuration (layer l seeded with torch.manual_seed(l))."""
 
 from __future__ import annotations
 

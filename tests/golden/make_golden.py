@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by running the REFERENCE's own code on CPU.
 
-Needs the reference checkout (default ``/root/reference``, override with
-``FLASH_MOE_REFERENCE``); it is imported unmodified.  Two sources are used:
+Needs a checkout of the reference project: pass its path as the first argument or in
+``FLASH_MOE_REFERENCE``; it is imported unmodified.  Two sources are used:
 
 * the eager module ``FlashMoE_Pytorch`` (flash_moe/modules/flash_moe.py:108-191),
   with ``cfg.mlp_bias = False`` set on the config object because the class reads
@@ -10,7 +10,7 @@ Needs the reference checkout (default ``/root/reference``, override with
   (``TRITON_INTERPRET=1``), float32 only, with the autotuner pinned to its first
   config (the interpreter cannot benchmark configs).
 
-Run:  python tests/golden/make_golden.py
+Run:  python tests/golden/make_golden.py <reference checkout>
 Writes ``*.npz`` files next to this script.  The tests only read those files.
 """
 
@@ -19,7 +19,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("FLASH_MOE_REFERENCE", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLASH_MOE_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("usage: make_golden.py <path to the flash-moe reference checkout>")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -152,7 +154,7 @@ def triton_mlp_case(name, T, H, I):
 
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count() or 1)
-    # eager module: a mini case stored with all inputs, and BASELINE config 1 stored as outputs + digest
+    # eager module: a mini case stored with all inputs, and benchmark configuration 1 stored as outputs + digest
     layer_case("eager_mini_fp32", 64, 128, 256, 4, False, 2, 16, torch.float32, store_inputs=True)
     layer_case("eager_mini_fp32_train_norm", 64, 128, 256, 4, True, 2, 16, torch.float32, store_inputs=True, train=True)
     layer_case("eager_mini_bf16", 64, 128, 256, 4, False, 2, 16, torch.bfloat16, store_inputs=True)

@@ -1,4 +1,4 @@
-"""The BASELINE configurations beyond the benchmarked one, as parity cases on the GPU.
+"""The benchmark configurations 3, 4 and 5 (the ones beyond the timed one), as parity cases on the GPU.
 
 Sizes the CPU oracle cannot brute-force are covered by size-independent properties plus exact
 comparison on a sample of tokens."""

@@ -60,7 +60,7 @@ def chained_checks(ref, x, y, logits, idx, gates, dtype, out_tol, strict=False):
 
 
 def test_layer_config1_fp32_matches_reference_fixture(golden_dir):
-    """BASELINE config 1 (T=256, H=256, I=1024, N=1024, k=8, fp32): against the output the
+    """Benchmark configuration 1 (T=256, H=256, I=1024, N=1024, k=8, fp32): against the output the
     reference's eager module produced for the same seeds."""
     z = np.load(os.path.join(golden_dir, "eager_c1_fp32.npz"))
     ref, ours = make_layer_pair(256, 1024, 1024, 8, False, torch.float32)
@@ -106,7 +106,7 @@ def test_layer_train_mode_batch_statistics():
 
 
 def test_layer_config2_full_size_bf16():
-    """BASELINE config 2 (T=4096, H=1024, I=4096, N=16384, k=64, bf16), teacher-forced output parity and
+    """Benchmark configuration 2 (T=4096, H=1024, I=4096, N=16384, k=64, bf16), teacher-forced output parity and
     the same result with the shared MLP on the main stream."""
     ref, ours = make_layer_pair(1024, 4096, 16384, 64, False, torch.bfloat16)
     ref.eval(); ours.eval()
