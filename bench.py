@@ -32,9 +32,24 @@ WORKLOAD = dict(name="config2: 1x4096 tokens, H=1024, I=4096, N=16384 (128x128 k
                 T=4096, H=1024, I=4096, N=16384, k=64, norm=False)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 L2_FLUSH_BYTES = 256 << 20
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# capture summarised in profiles/gemm_swiglu_config2.md (25.199 MB read + 0.184 MB written)
-DOMINANT_KERNEL_DRAM_BYTES = 25383424
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel of the layer at this
+# workload, from the ncu captures summarised in profiles/*_config2.md
+NCU_DRAM_BYTES = {
+    "router_front": 8404992 + 8931072,  # bn_apply + router GEMM
+    "router_topk": 2168576,
+    "expert_scores": 44577024 + 57088,
+    "expert_accum": 36716544 + 321024,
+    "mlp_up": 25196032 + 64256,
+    "mlp_down": 58740224 + 1576960,
+}
+KERNEL_OF_STAGE = {
+    "router_front": "bn_apply_kernel + gemm_tcgen05_kernel<128, ROUTER> (batch-norm, sub-key logits)",
+    "router_topk": "router_topk_reg_kernel<bf16, 4> (log-softmax, product-key top-k, gates)",
+    "expert_scores": "expert_scores_mma_kernel<bf16, 8> (gathered down rows x token row, silu * gate)",
+    "expert_accum": "expert_accum_kernel<bf16, float, 2> (gate-weighted sum of gathered up rows)",
+    "mlp_up": "gemm_tcgen05_pair_kernel<SWIGLU> (shared MLP gate/up GEMM + SiLU*up epilogue, CTA pairs)",
+    "mlp_down": "gemm_tcgen05_pair_kernel<ADD> (shared MLP down GEMM + fp32 expert addend, CTA pairs)",
+}
 
 
 def load_peaks():
@@ -276,6 +291,8 @@ def main():
             layer(x_dev)
         serial_ms, _, stage_ms = timed_pass(args.steps, True)
         layer.overlap_shared_mlp = was
+        layer(x_dev, return_routing=True)
+        distinct_experts = int(torch.unique(layer.last_indices).numel())
     check_status()
 
     # ---------------- end to end: pinned host in, pinned host out, copies inside the timed region ----
@@ -328,9 +345,34 @@ def main():
 
     if rank == 0:
         peaks, peak_kind = load_peaks()
-        up_flops = 2.0 * T * (2 * I) * H
-        up_ms = stage_ms["mlp_up"]
-        achieved = up_flops / (up_ms * 1e-3) / 1e12
+        # per-kernel rooflines: algorithmic flops (tensor-bound GEMMs) or algorithmic HBM bytes (the rest;
+        # intermediates such as h, gs and the fp32 accumulator are not algorithmic) over the stage's
+        # CUDA-event duration.  U = distinct experts the router selected in this batch.
+        P, U, nk = T * k, distinct_experts, w_nk()
+        work = {
+            "router_front": ("tensor", 4.0 * T * H * nk),
+            "router_topk": ("hbm", 2.0 * T * 2 * nk + 8.0 * P + 2.0 * P + 2.0 * P),
+            "expert_scores": ("hbm", 2.0 * U * H + 2.0 * T * H + 8.0 * P + 2.0 * P),
+            "expert_accum": ("hbm", 2.0 * U * H + 8.0 * P),
+            "mlp_up": ("tensor", 2.0 * T * (2 * I) * H),
+            "mlp_down": ("tensor", 2.0 * T * H * I),
+        }
+        kernel_rooflines = {}
+        for name, (bound, amount) in work.items():
+            rate = amount / (stage_ms[name] * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+            peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
+            kernel_rooflines[name] = {
+                "kernel": KERNEL_OF_STAGE[name], "bound": bound, "achieved": round(rate, 2), "peak": peak,
+                "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": round(rate / peak, 4),
+                "traffic": NCU_DRAM_BYTES[name], "ms": round(stage_ms[name], 4),
+                "peak_source": peak_kind + (" (burst)" if bound == "tensor" else "")}
+        dominant = max(stage_ms, key=lambda n: stage_ms[n])
+        # the two expert passes move P*H*2 bytes of gathered table rows from L2 to the SMs, which is what
+        # bounds them once the tables sit in L2; report that rate beside the HBM figure
+        for name in ("expert_scores", "expert_accum"):
+            kernel_rooflines[name]["l2_gather_gbs"] = round(2.0 * P * H / (stage_ms[name] * 1e-3) / 1e9, 1)
+            kernel_rooflines[name]["l2_gather_note"] = ("tables are L2-resident: P*H*2 B of gathered rows cross L2->SM per "
+                                                        "launch; a load-only microbenchmark of this pattern reaches ~15000 GB/s")
         # whole-layer roofline: sum of the stage bounds (tensor pipe for the GEMMs, HBM for the rest)
         tensor_flops = 4.0 * T * H * w_nk() + 6.0 * T * H * I
         hbm_bytes = 2 * T * H * 2 + 4 * T * w_nk() + 4 * w_nk() * H + 6 * H * I + 4 * N * H
@@ -343,14 +385,14 @@ def main():
                        "l2": "flushed between timed steps (256 MiB write)",
                        "overlap_shared_mlp": bool(layer.overlap_shared_mlp),
                        "launch": "eager module calls" if args.eager else "CUDA graph replay (GraphedFlashMoE)"},
-            "stage_ms": {n: round(v, 4) for n, v in stage_ms.items()},
+            "stage_ms": dict({n: round(v, 4) for n, v in stage_ms.items()},
+                             experts=round(stage_ms["expert_scores"] + stage_ms["expert_accum"], 4)),
             "stage_ms_note": "second timed pass with the shared MLP on the main stream (no overlap): "
                              f"{round(serial_ms, 4)} ms/step",
             "layer_roofline": {"bound_ms": round(bound_ms, 4), "frac": round(bound_ms / ms, 4), "peaks": peak_kind},
-            "roofline": {"kernel": "gemm_tcgen05_kernel<256, SWIGLU> (shared MLP gate/up GEMM + SiLU*up epilogue)",
-                         "bound": "tensor", "achieved": round(achieved, 2), "peak": peaks["bf16_tflops"],
-                         "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
-                         "traffic": DOMINANT_KERNEL_DRAM_BYTES, "peak_source": peak_kind + " (burst)"},
+            "roofline": dict(kernel_rooflines[dominant], choice="the kernel with the longest measured duration"),
+            "kernel_rooflines": kernel_rooflines,
+            "distinct_experts_selected": distinct_experts,
             "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
                     "d2h_bytes_per_step": y_host[0].numel() * y_host[0].element_size()},

@@ -16,11 +16,12 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libfmoe_sm100a.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
-NUM_STAGES = 5
-STAGE_NAMES = ("router_front", "router_topk", "experts", "mlp_up", "mlp_down")
+NUM_STAGES = 6
+STAGE_NAMES = ("router_front", "router_topk", "expert_scores", "expert_accum", "mlp_up", "mlp_down")
 
 STATUS_BAD_EXPERT_ID = 1
 STATUS_WAIT_TIMEOUT = 2
+STATUS_BAD_ROW_INDEX = 4
 
 
 class FmoeError(RuntimeError):
@@ -79,6 +80,7 @@ SIGNATURES = {
     "fmoe_router_front": (_I, [_P, _P, _P, _P, _I, _F, _F, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_bn_batch_sums_workspace_bytes": (_Z, [_I]),
     "fmoe_bn_batch_sums": (_I, [_P, _I, _L, _I, _P, _P, _Z, _P]),
+    "fmoe_combine_partial_rows": (_I, [_P, _L, _P, _I, _L, _I, _P, _P, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_expert_static_scratch_bytes": (_Z, []),
@@ -172,3 +174,5 @@ def check_status(device=None) -> None:
         raise FmoeError("a device-side wait timed out inside a flash_moe_b200 kernel")
     if v & STATUS_BAD_EXPERT_ID:
         raise FmoeError("expert index outside [0, num_experts) was skipped")
+    if v & STATUS_BAD_ROW_INDEX:
+        raise FmoeError("combine_partial_rows skipped a slot that points past the received rows")

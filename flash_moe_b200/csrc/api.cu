@@ -181,6 +181,12 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
                         static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,
+                              int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream) {
+  return launch_combine_rows(rows, num_rows, slot, num_sources, num_tokens, hidden, out, status,
+                             static_cast<cudaStream_t>(stream));
+}
+
 size_t fmoe_expert_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k) {
   return expert_workspace_bytes(num_tokens, hidden, num_experts, top_k);
 }
@@ -291,13 +297,23 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   }
   if (rc != FMOE_OK) return rc;
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 1, s);
-  FMOE_MARK(FMOE_STAGE_EXPERTS, 0, s);
+  FMOE_MARK(FMOE_STAGE_EXPERT_SCORES, 0, s);
 
-  // routed experts into an fp32 accumulator
+  // routed experts into an fp32 accumulator; the scores stage ends and the accumulate stage starts
+  // between the two passes, inside the launcher
+  void* between[2] = {nullptr, nullptr};
+  if (a->stage_events != nullptr) {
+    between[0] = a->stage_events[2 * FMOE_STAGE_EXPERT_SCORES + 1];
+    between[1] = a->stage_events[2 * FMOE_STAGE_EXPERT_ACCUM + 0];
+    if (T == 0 || k == 0) {  // the launcher returns before it reaches the marks
+      FMOE_MARK(FMOE_STAGE_EXPERT_SCORES, 1, s);
+      FMOE_MARK(FMOE_STAGE_EXPERT_ACCUM, 0, s);
+    }
+  }
   rc = launch_expert_forward(a->x, a->down_embed, a->up_embed, indices, gates, w.acc, dtype, FMOE_DTYPE_F32, T, H, N, k,
-                             w.expert, w.expert_bytes, a->status, s);
+                             w.expert, w.expert_bytes, a->status, s, between);
   if (rc != FMOE_OK) return rc;
-  FMOE_MARK(FMOE_STAGE_EXPERTS, 1, s);
+  FMOE_MARK(FMOE_STAGE_EXPERT_ACCUM, 1, s);
 
   if (fj != nullptr) {
     FMOE_CUDA_TRY(cudaStreamWaitEvent(s, fj->join, 0));

@@ -115,7 +115,9 @@ int launch_router_topk(const void* log_probs, int dtype, int64_t T, int nk, int 
 size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k);
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
-                          size_t ws_bytes, int32_t* status, cudaStream_t stream);
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr);
+// between_passes (nullable): two cudaEvent_t handles (each nullable) recorded back to back after the scores pass
+// and before the accumulate pass.
 
 // C[M,N] = A[M,K] * B[N,K]^T on tcgen05 with a fused epilogue (gemm_sm100.cu); bf16/fp16 only.
 int launch_gemm_swiglu(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I, int K,
@@ -139,5 +141,7 @@ int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1,
 
 // elementwise.cu
 int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, int64_t T, int nk, cudaStream_t stream);
+int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
+                        float* out, int32_t* status, cudaStream_t stream);
 
 }  // namespace fmoe

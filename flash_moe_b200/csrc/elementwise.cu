@@ -182,6 +182,37 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
   return FMOE_OK;
 }
 
+// out[t] = sum over sources g of rows[slot[g * ntok + t]] (slot < 0: source g holds nothing for token t).
+// One thread per 16 bytes of an output row; sources are added in ascending g, so the sum is reproducible.
+__global__ void __launch_bounds__(256) combine_rows_kernel(const float4* __restrict__ rows, int64_t num_rows,
+                                                           const int32_t* __restrict__ slot, int num_sources,
+                                                           int64_t ntok, int h4, float4* __restrict__ out,
+                                                           int32_t* status) {
+  const int64_t total = ntok * h4;
+  bool bad = false;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / h4;
+    const int c = static_cast<int>(i - t * h4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int g = 0; g < num_sources; ++g) {
+      const int64_t r = slot[static_cast<int64_t>(g) * ntok + t];
+      if (r < 0) continue;
+      if (r >= num_rows) {
+        bad = true;
+        continue;
+      }
+      const float4 v = __ldg(rows + r * h4 + c);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    out[i] = acc;
+  }
+  if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_ROW_INDEX);
+}
+
 }  // namespace
 
 size_t bn_workspace_bytes(int H) { return static_cast<size_t>(2 * kBnSplits + 2) * H * sizeof(float); }
@@ -236,6 +267,22 @@ int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, in
       break;
     default: return FMOE_ERR_BAD_ARG;
   }
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
+                        float* out, int32_t* status, cudaStream_t stream) {
+  if (num_rows < 0 || num_sources < 0 || ntok < 0 || H <= 0) return FMOE_ERR_BAD_ARG;
+  if (ntok == 0) return FMOE_OK;
+  if (out == nullptr || (num_sources > 0 && slot == nullptr) || (num_rows > 0 && rows == nullptr)) return FMOE_ERR_BAD_ARG;
+  if (H % 4 != 0 || !aligned16(rows) || !aligned16(out)) return FMOE_ERR_ALIGNMENT;
+  const int h4 = H / 4;
+  const int64_t want = (ntok * h4 + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  combine_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(rows), num_rows, slot, num_sources, ntok,
+                                                h4, reinterpret_cast<float4*>(out), status);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }

@@ -465,7 +465,7 @@ void launch_accum(const void* up, const int64_t* idx, const ExpertWs& w, void* o
 template <typename T>
 int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
               int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
-              cudaStream_t stream) {
+              cudaStream_t stream, void* const* between_passes) {
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
@@ -519,6 +519,9 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
     else launch_scores<T, 0>(x, down, w, N, gates, H, k, P, stream);
     FMOE_LAUNCH_CHECK();
   }
+  if (between_passes != nullptr)
+    for (int i = 0; i < 2; ++i)
+      if (between_passes[i] != nullptr) FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(between_passes[i]), stream));
 
 #define FMOE_ACCUM(NCH_)                                                                       \
   do {                                                                                         \
@@ -543,7 +546,7 @@ size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k) {
 
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
-                          size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes) {
   if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
   if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
   if (T == 0) return FMOE_OK;
@@ -562,11 +565,13 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
   const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
   switch (dtype) {
     case FMOE_DTYPE_F32:
-      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream);
+      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes);
     case FMOE_DTYPE_BF16:
-      return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream);
+      return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
+                                      between_passes);
     case FMOE_DTYPE_F16:
-      return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream);
+      return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
+                                      between_passes);
     default:
       return FMOE_ERR_BAD_ARG;
   }

@@ -55,4 +55,24 @@ def flash_expert_fp32(hidden_states, down_weights, up_weights, indices, routing_
     return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, torch.float32)
 
 
+def combine_partial_rows(rows, slot, num_tokens):
+    """out[t] = sum_g rows[slot[g, t]] (slot < 0 skipped), float32; the combine step of the expert-sharded layout.
+
+    rows [R, H] float32 (partial sums received from the ranks that own the experts), slot [G, num_tokens] int32.
+    """
+    dev = _lib.require_cuda(rows, slot)
+    rows, slot = contiguous(rows), contiguous(slot)
+    if rows.dtype != torch.float32 or slot.dtype != torch.int32 or rows.dim() != 2 or slot.dim() != 2:
+        raise _lib.FmoeError("expected rows[R,H] float32 and slot[G,T] int32")
+    if slot.shape[1] != num_tokens:
+        raise _lib.FmoeError("slot must have one column per token")
+    out = torch.empty((num_tokens, rows.shape[1]), device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fmoe_combine_partial_rows(
+            rows.data_ptr(), rows.shape[0], slot.data_ptr(), slot.shape[0], num_tokens, rows.shape[1], out.data_ptr(),
+            _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev))
+    _lib.check(rc, "fmoe_combine_partial_rows")
+    return out
+
+
 triton_flash_expert_func = flash_expert_func

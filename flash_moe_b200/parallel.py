@@ -40,8 +40,9 @@ def plan_dispatch(indices: torch.Tensor, gates: torch.Tensor, num_experts: int, 
 
     Returns `(counts, token_ids, local_ids, local_gates)`: `counts[g]` tokens go to rank g;
     `token_ids` lists them destination by destination; `local_ids/local_gates [sum(counts), k]` hold,
-    per sent token, its slots owned by that destination (local expert id, gate) and (0, 0) elsewhere -
-    a zero gate makes the padded slot contribute nothing.  Ids outside [0, num_experts) are dropped.
+    per sent token, its slots owned by that destination (local expert id, gate); the other slots carry
+    gate 0, so they contribute nothing, and repeat one of the token's own local ids so that padding does
+    not pile up on a single expert row.  Ids outside [0, num_experts) are dropped.
     """
     valid = (indices >= 0) & (indices < num_experts)
     dest = torch.where(valid, indices % world, torch.full_like(indices, -1))
@@ -53,7 +54,8 @@ def plan_dispatch(indices: torch.Tensor, gates: torch.Tensor, num_experts: int, 
         tok = m.any(dim=1).nonzero(as_tuple=True)[0]
         counts.append(int(tok.numel()))
         tok_l.append(tok)
-        id_l.append(torch.where(m, local, torch.zeros_like(local))[tok])
+        own = torch.where(m, local, torch.full_like(local, -1))[tok]
+        id_l.append(torch.where(own >= 0, own, own.max(dim=1, keepdim=True).values))
         gate_l.append(torch.where(m, gates, zero_g)[tok])
     return counts, torch.cat(tok_l), torch.cat(id_l), torch.cat(gate_l)
 
@@ -67,12 +69,14 @@ def _all_to_all(t: torch.Tensor, recv_rows: int, out_splits: List[int], in_split
 class ExpertShardedExperts:
     """Fine-grained experts with the tables sharded over the ranks of `group` (see module docstring).
 
-    `expert_fn(x, down, up, indices, gates) -> float32 [rows, H]` evaluates local experts; the default is
-    the CUDA op of this package; CPU tests pass a stand-in with the same signature.
+    `expert_fn(x, down, up, indices, gates) -> float32 [rows, H]` evaluates local experts and
+    `combine_fn(rows, slot, num_tokens) -> float32 [num_tokens, H]` sums the returned partial rows
+    (`slot[g, t]` = row that rank g returned for token t, -1 if none); the defaults are the CUDA ops of this
+    package; CPU tests pass stand-ins with the same signatures.
     """
 
     def __init__(self, down_shard: torch.Tensor, up_shard: torch.Tensor, num_experts: int, group=None,
-                 expert_fn: Optional[Callable] = None):
+                 expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None):
         self.down, self.up = down_shard, up_shard
         self.num_experts = num_experts
         self.group = group
@@ -80,7 +84,10 @@ class ExpertShardedExperts:
         self.rank = dist.get_rank(group)
         if expert_fn is None:
             from .ops.flash_expert import flash_expert_fp32 as expert_fn
+        if combine_fn is None:
+            from .ops.flash_expert import combine_partial_rows as combine_fn
         self.expert_fn = expert_fn
+        self.combine_fn = combine_fn
         self.last_stats = {}
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, gates: torch.Tensor) -> torch.Tensor:
@@ -100,8 +107,13 @@ class ExpertShardedExperts:
         else:
             partial = torch.zeros((0, x.shape[1]), dtype=torch.float32, device=x.device)
         back = _all_to_all(partial, sum(counts), counts, recv, group)
-        out = torch.zeros((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
-        out.index_add_(0, tok, back)
+        # slot[g, t] = position in `back` of the row rank g returned for token t (rows come back in the order sent)
+        sent = sum(counts)
+        owner = torch.repeat_interleave(torch.arange(world, device=x.device),
+                                        torch.tensor(counts, device=x.device), output_size=sent)
+        slot = torch.full((world, x.shape[0]), -1, dtype=torch.int32, device=x.device)
+        slot[owner, tok] = torch.arange(sent, dtype=torch.int32, device=x.device)
+        out = self.combine_fn(back, slot, x.shape[0])
         self.last_stats = {"sent_rows": sum(counts), "received_rows": rows,
                            "dispatch_bytes": sum(counts) * x.shape[1] * x.element_size(),
                            "combine_bytes": rows * x.shape[1] * 4}

@@ -42,7 +42,8 @@ enum fmoe_error {
 
 enum fmoe_status_bits {
   FMOE_STATUS_BAD_EXPERT_ID = 1, /* an index outside [0, num_experts) was skipped */
-  FMOE_STATUS_WAIT_TIMEOUT = 2   /* a bounded device-side wait gave up */
+  FMOE_STATUS_WAIT_TIMEOUT = 2,  /* a bounded device-side wait gave up */
+  FMOE_STATUS_BAD_ROW_INDEX = 4  /* fmoe_combine_partial_rows skipped a slot >= num_rows */
 };
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -105,6 +106,17 @@ int fmoe_expert_forward(const void* x, const void* down, const void* up, const i
                         int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * Combine step of the expert-sharded layout (tables split over GPUs by expert id, token rows sent to
+ * the owners, partial results sent back): out[t] = sum_g rows[slot[g * num_tokens + t]], skipping
+ * slot < 0, sources added in ascending g in float32.  rows [num_rows, hidden] float32 are the partial
+ * sums received from the owners, slot [num_sources, num_tokens] int32 maps (owner, token) to its row.
+ * The reference has no multi-GPU code; this finishes the sum of flash_expert.py:13-211 when the
+ * experts of one token live on several GPUs.  hidden must be a multiple of 4.
+ */
+int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,
+                              int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream);
+
+/*
  * fmoe_expert_forward without a caller-supplied workspace.  It has no counterpart in the
  * reference; it exists for hosts that cannot allocate device memory where they call the library
  * (a frozen memory plan after warm-up, a fixed real-time budget, a language binding without a
@@ -146,10 +158,11 @@ int fmoe_mlp_forward(const void* x, const void* gate_w, const void* up_w, const 
 enum fmoe_stage {
   FMOE_STAGE_ROUTER_FRONT = 0, /* batch-norm + sub-key GEMM + log-softmax */
   FMOE_STAGE_ROUTER_TOPK = 1,
-  FMOE_STAGE_EXPERTS = 2,
-  FMOE_STAGE_MLP_UP = 3,   /* h = silu(x Wg^T) * (x Wu^T) */
-  FMOE_STAGE_MLP_DOWN = 4, /* y = h Wd^T + experts */
-  FMOE_NUM_STAGES = 5
+  FMOE_STAGE_EXPERT_SCORES = 2, /* (sort +) gs = silu(<x, down[e]>) * gate */
+  FMOE_STAGE_EXPERT_ACCUM = 3,  /* acc = sum gs * up[e] */
+  FMOE_STAGE_MLP_UP = 4,        /* h = silu(x Wg^T) * (x Wu^T) */
+  FMOE_STAGE_MLP_DOWN = 5,      /* y = h Wd^T + acc */
+  FMOE_NUM_STAGES = 6
 };
 
 typedef struct fmoe_layer_args {

@@ -130,3 +130,27 @@ def test_mlp_matches_reference_kernel_fixture(golden_dir):
     t = {n: torch.from_numpy(z[n]).cuda() for n in z.files}
     got = flash_mlp_func(t["x"], t["wg"], t["wu"], t["wd"])
     np.testing.assert_allclose(got.cpu().numpy(), z["y"], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("T,H,G", [(1, 4, 1), (37, 64, 3), (513, 2048, 8)])
+def test_combine_partial_rows_sums_in_source_order(T, H, G):
+    """fmoe_combine_partial_rows: out[t] = sum_g rows[slot[g, t]] in float32, ascending g, -1 skipped - bit exact."""
+    from flash_moe_b200 import check_status
+    from flash_moe_b200.ops.flash_expert import combine_partial_rows
+
+    g = torch.Generator().manual_seed(T + H)
+    present = torch.rand(G, T, generator=g) < 0.6
+    R = int(present.sum())
+    slot = torch.full((G, T), -1, dtype=torch.int32)
+    slot[present] = torch.randperm(R, generator=g).to(torch.int32)
+    rows = torch.randn(R + 3, H, generator=g)  # three rows nobody points at
+    want = torch.zeros(T, H)
+    for s in range(G):
+        m = slot[s] >= 0
+        want[m] = want[m] + rows[slot[s][m].long()]
+    got = combine_partial_rows(rows.cuda(), slot.cuda(), T)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(got.cpu(), want)
+    with pytest.raises(Exception):
+        combine_partial_rows(rows.cuda().to(torch.bfloat16), slot.cuda(), T)

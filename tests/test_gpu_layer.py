@@ -150,3 +150,29 @@ def test_cuda_graph_replay_matches_eager():
     check_status()
     assert torch.equal(y, y2) and torch.equal(logits, logits2)
     assert torch.equal(y3, want3)
+
+
+def test_stage_events_cover_the_forward():
+    """The library records an event pair per stage (enum fmoe_stage); the stages follow one another on the stream."""
+    from flash_moe_b200 import StageTimer, _lib
+
+    ref, ours = make_layer_pair(256, 512, 1024, 8, False, torch.bfloat16)
+    ours.eval()
+    x = randn((1, 512, 256), 6, torch.bfloat16).cuda()
+    timer = StageTimer()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.no_grad():
+        ours(x)
+        start.record()
+        y, _ = ours(x, stage_timer=timer)
+        end.record()
+        want, _ = ours(x)
+    torch.cuda.synchronize()
+    ms = timer.elapsed_ms()
+    assert tuple(ms) == _lib.STAGE_NAMES and len(ms) == 6
+    assert all(v > 0 for v in ms.values())
+    assert sum(ms.values()) <= start.elapsed_time(end) * 1.05
+    ev = timer.events  # end of one stage is not after the start of the next
+    for i in range(5):
+        assert ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) >= 0
+    assert torch.equal(y, want)

@@ -44,6 +44,8 @@ def test_plan_dispatch_sends_each_token_once_per_owner():
             mine = [(int(e) // world, float(w)) for e, w in zip(idx[token], gates[token]) if 0 <= e < N and e % world == dest]
             got = [(int(e), float(w)) for e, w in zip(ids[off + row], gts[off + row]) if w != 0]
             assert sorted(mine) == sorted(got)
+            # padded slots (gate 0) repeat one of the token's own local ids instead of piling up on id 0
+            assert {int(e) for e in ids[off + row]} == {e for e, _ in mine}
             total_pairs += len(mine)
         off += c
     assert total_pairs == int(((idx >= 0) & (idx < N)).sum())
@@ -69,8 +71,16 @@ WORKER = textwrap.dedent(
     gates = torch.softmax(torch.randn(T, k, generator=g), -1)
     want = O.expert_forward(x, down, up, idx, gates)
     s, e = token_shard(T, rank, world)
+
+    def combine(rows, slot, ntok):  # CPU stand-in of combine_partial_rows
+        out = torch.zeros(ntok, rows.shape[1])
+        for g_ in range(slot.shape[0]):
+            m = slot[g_] >= 0
+            out[m] += rows[slot[g_][m].long()]
+        return out
+
     layer = ExpertShardedExperts(shard_expert_table(down, rank, world), shard_expert_table(up, rank, world), N,
-                                 expert_fn=O.expert_forward)
+                                 expert_fn=O.expert_forward, combine_fn=combine)
     got = layer.forward(x[s:e], idx[s:e], gates[s:e])
     err = (got - want[s:e]).abs().max().item()
     assert err < 1e-5, err
