@@ -197,12 +197,68 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+def run_reference_gpu_arm(args):
+    """Informational third arm: the UNMODIFIED reference package (its Triton `FlashMoE` module), when an
+    install of it sits in baseline/_ref, timed on cuda:0 at the same workload with the same timing rules.
+    It is not the reference arm of the bench contract (that one is the CPU path above)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "flash_moe")):
+            raise RuntimeError("no reference install under baseline/_ref")
+        sys.path.insert(0, ref_dir)
+        from flash_moe.modules.flash_moe import FlashMoE as RefFlashMoE, FlashMoEConfig as RefConfig
+
+        w = WORKLOAD
+        T = w["T"]
+        dev = torch.device("cuda", 0)
+        torch.manual_seed(0)
+        ref = RefFlashMoE(RefConfig(w["H"], w["I"], "silu", w["N"], w["k"], w["norm"])).to(torch.bfloat16).to(dev).eval()
+        x_host = torch.randn(1, T, w["H"], generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+        y_host = torch.empty_like(x_host).pin_memory()
+        x_dev = x_host.to(dev)
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        with torch.no_grad():
+            for _ in range(args.warmup):  # includes Triton's JIT and autotuning
+                ref(x_dev)
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(args.steps):
+                flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                ref(x_dev)
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+            ms = sum(times) / len(times)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                x_dev.copy_(x_host, non_blocking=True)
+                y, _ = ref(x_dev)
+                y_host.copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
+            e2e_ms = 1e3 * (time.perf_counter() - t0) / args.steps
+        print(json.dumps({
+            "impl": "reference-gpu", "metric": METRIC, "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "arm": "unmodified reference FlashMoE (Triton kernels + cuBLAS) from baseline/_ref",
+                       "l2": "flushed between timed steps (256 MiB write)"},
+            "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": y_host.numel() * 2}}))
+    except Exception as e:  # noqa: BLE001 - any failure of the foreign package is reported, not raised
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="(default) run the shared MLP on the main stream")
     ap.add_argument("--overlap", action="store_true", help="fork the shared-MLP up GEMM to a side stream")
@@ -212,6 +268,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.impl == "reference-gpu":
+        run_reference_gpu_arm(args)
         return
 
     import torch.distributed as dist

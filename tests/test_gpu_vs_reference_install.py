@@ -1,0 +1,125 @@
+"""Ours against the UNMODIFIED reference package running its Triton kernels on the same GPU.
+
+Needs an install of the reference under baseline/_ref (`pip install --no-deps --target baseline/_ref <checkout>`;
+the folder is git-ignored) - skipped when it is absent.  The golden fixtures pin the oracle against the reference
+on CPU; these cases close the loop on the device at sizes the interpreter cannot reach.
+"""
+
+import os
+import sys
+
+import pytest
+import torch
+
+from oracle import flashmoe_oracle as O
+from tests.helpers import randn
+
+pytestmark = pytest.mark.gpu
+REF_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+
+
+@pytest.fixture(scope="module")
+def ref_pkg():
+    if not os.path.isdir(os.path.join(REF_DIR, "flash_moe")):
+        pytest.skip("no reference install under baseline/_ref")
+    sys.path.insert(0, REF_DIR)
+    try:
+        import flash_moe.modules.flash_moe as ref_module
+        import flash_moe.ops.triton.flash_expert as ref_expert
+        import flash_moe.ops.triton.flash_mlp as ref_mlp
+        import flash_moe.ops.triton.flash_router as ref_router
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"reference install does not import: {e!r}")
+    finally:
+        sys.path.remove(REF_DIR)
+    return ref_module, ref_router, ref_expert, ref_mlp
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,nk,k", [(64, 16, 4), (300, 128, 64), (4096, 128, 64), (128, 256, 32)])
+def test_router_bit_exact_against_reference_triton(ref_pkg, dtype, T, nk, k):
+    from flash_moe_b200.ops.flash_router import triton_flash_router_func as ours
+
+    _, ref_router, _, _ = ref_pkg
+    lp = torch.log_softmax(randn((2, T, nk), 3 + T, torch.float32), -1).to(dtype).cuda()
+    s_ref, i_ref = ref_router.triton_flash_router_func(lp, nk, k)
+    s, i = ours(lp, nk, k)
+    torch.cuda.synchronize()
+    assert torch.equal(i, i_ref)
+    assert torch.equal(s, s_ref)
+
+
+def test_router_ties_against_reference_triton(ref_pkg):
+    from flash_moe_b200.ops.flash_router import triton_flash_router_func as ours
+
+    _, ref_router, _, _ = ref_pkg
+    raw = torch.round(randn((2, 512, 64), 9, torch.float32) * 2) / 2 - 4.0  # coarse grid: many equal sums
+    for dtype in (torch.float32, torch.bfloat16):
+        lp = raw.to(dtype).cuda()
+        s_ref, i_ref = ref_router.triton_flash_router_func(lp, 64, 16)
+        s, i = ours(lp, 64, 16)
+        torch.cuda.synchronize()
+        assert torch.equal(s, s_ref) and torch.equal(i, i_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_expert_and_mlp_ops_against_reference_triton(ref_pkg, dtype):
+    from flash_moe_b200.ops.flash_expert import triton_flash_expert_func as our_expert
+    from flash_moe_b200.ops.flash_mlp import triton_flash_mlp_func as our_mlp
+
+    _, _, ref_expert, ref_mlp = ref_pkg
+    T, H, I, N, k = 512, 256, 512, 4096, 16
+    x = (randn((T, H), 1, torch.float32) * 0.5).to(dtype).cuda()
+    down = (randn((N, H), 2, torch.float32) * 0.1).to(dtype).cuda()
+    up = (randn((N, H), 3, torch.float32) * 0.1).to(dtype).cuda()
+    idx = torch.randint(0, N, (T, k), generator=torch.Generator().manual_seed(4)).cuda()
+    gates = torch.softmax(randn((T, k), 5, torch.float32), -1).to(dtype).cuda()
+    want = O.expert_forward(x.cpu(), down.cpu(), up.cpu(), idx.cpu(), gates.cpu())  # float32 evaluation
+    got_ref = ref_expert.triton_flash_expert_func(x, down, up, idx, gates).float().cpu()
+    got = our_expert(x, down, up, idx, gates).float().cpu()
+    rms = want.pow(2).mean().sqrt()
+    err_ours, err_ref = (got - want).abs().max() / rms, (got_ref - want).abs().max() / rms
+    print("expert max|err|/RMS vs fp32: ours", float(err_ours), "reference", float(err_ref))
+    assert err_ours <= max(2e-2, 1.05 * float(err_ref))  # at least as close to the exact sum as the reference's kernel
+    wg = (randn((I, H), 6, torch.float32) * 0.05).to(dtype).cuda()
+    wu = (randn((I, H), 7, torch.float32) * 0.05).to(dtype).cuda()
+    wd = (randn((H, I), 8, torch.float32) * 0.05).to(dtype).cuda()
+    want = O.mlp_forward(x.cpu(), wg.cpu(), wu.cpu(), wd.cpu())
+    got_ref = ref_mlp.triton_flash_mlp_func(x, wg, wu, wd).float().cpu()
+    got = our_mlp(x, wg, wu, wd).float().cpu()
+    rms = want.pow(2).mean().sqrt()
+    err_ours, err_ref = (got - want).abs().max() / rms, (got_ref - want).abs().max() / rms
+    print("mlp max|err|/RMS vs fp32: ours", float(err_ours), "reference", float(err_ref))
+    assert err_ours <= max(2e-2, 1.05 * float(err_ref))
+
+
+def test_layer_against_reference_module_config2(ref_pkg):
+    """Benchmark configuration 2, same seeded parameters: identical router logits, the same experts for nearly
+    every token, and an output no further from the float32 evaluation than the reference's own."""
+    from flash_moe_b200 import FlashMoE, FlashMoEConfig, check_status
+
+    ref_module, _, _, _ = ref_pkg
+    cfg = (1024, 4096, "silu", 16384, 64, False)
+    torch.manual_seed(0)
+    ref = ref_module.FlashMoE(ref_module.FlashMoEConfig(*cfg)).to(torch.bfloat16).cuda().eval()
+    ours = FlashMoE(FlashMoEConfig(*cfg)).to(torch.bfloat16).cuda().eval()
+    ours.load_state_dict(ref.state_dict())
+    x = randn((1, 4096, 1024), 1, torch.bfloat16).cuda()
+    with torch.no_grad():
+        y_ref, logits_ref = ref(x)
+        y, logits = ours(x, return_routing=True)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(logits, logits_ref)
+    # exact output for the routing OUR layer chose, float32 on the CPU
+    oracle = O.OracleFlashMoE(1024, 4096, 16384, 64, False)
+    oracle.load_state_dict({k_: v.float().cpu() for k_, v in ref.state_dict().items()})
+    with torch.no_grad():
+        want = oracle.forward_fp32_given_routing(x.cpu().float().view(-1, 1024), ours.last_indices.cpu(),
+                                                 ours.last_gates.float().cpu(), round_h_to=torch.bfloat16).view(1, 4096, 1024)
+    rms = want.pow(2).mean().sqrt()
+    err_ours = float((y.float().cpu() - want).abs().max() / rms)
+    rms_diff = float((y.float() - y_ref.float()).pow(2).mean().sqrt() / y_ref.float().pow(2).mean().sqrt())
+    print("config 2: ours vs fp32", err_ours, " rms(ours - reference)/rms", rms_diff)
+    assert err_ours < 3e-2
+    assert rms_diff < 2e-2
