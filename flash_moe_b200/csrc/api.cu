@@ -181,6 +181,32 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
                         static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_router_topk_backward(const void* dscores, const int64_t* indices, int dtype, int64_t num_tokens, int num_keys,
+                              int top_k, void* dlog_probs, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_router_topk_backward(dscores, indices, dtype, num_tokens, num_keys, top_k, dlog_probs,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+size_t fmoe_expert_backward_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k) {
+  return expert_backward_workspace_bytes(num_tokens, hidden, num_experts, top_k);
+}
+
+int fmoe_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
+                         const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype,
+                         int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                         size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_expert_backward(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, dtype, num_tokens, hidden,
+                                num_experts, top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
+                         int64_t num_elements, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_swiglu_backward(dh, a, b, da, db, h, dtype, num_elements, static_cast<cudaStream_t>(stream));
+}
+
 int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,
                               int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream) {
   return launch_combine_rows(rows, num_rows, slot, num_sources, num_tokens, hidden, out, status,

@@ -141,6 +141,14 @@ int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1,
 
 // elementwise.cu
 int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, int64_t T, int nk, cudaStream_t stream);
+size_t expert_backward_workspace_bytes(int64_t T, int H, int64_t N, int k);
+int launch_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
+                           const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype, int64_t T,
+                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream);
+int launch_router_topk_backward(const void* dscores, const int64_t* indices, int dtype, int64_t T, int nk, int k,
+                                void* dlog_probs, cudaStream_t stream);
+int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
+                           int64_t n, cudaStream_t stream);
 int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
                         float* out, int32_t* status, cudaStream_t stream);
 

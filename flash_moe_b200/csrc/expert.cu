@@ -16,6 +16,8 @@
 //   Both store gs = silu(s) * gate at the pair's (token, slot) position (4 bytes per pair).
 //   3. accumulate pass per token: out[t] = sum_j gs[t,j] * U[e_tj] in fp32 (packed f32x2 FMAs),
 //      fixed slot order, one rounding on store - no atomics, run-to-run deterministic.
+#include <cub/device/device_radix_sort.cuh>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
       }
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFull, acc, d);
-      if (lane == 0) gs[p] = silu_f32(acc) * to_f32<T>(gates[p]);
+      if (lane == 0) gs[p] = gates != nullptr ? silu_f32(acc) * to_f32<T>(gates[p]) : acc;  // nullptr: raw dot product
     }
   }
 }
@@ -302,8 +304,13 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
       }
     }
     if (tq == 0) {
-      if (ja < k) gs[t * k + ja] = oka ? silu_f32(c[0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
-      if (jb < k) gs[t * k + jb] = okb ? silu_f32(c[2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
+      if (gates != nullptr) {
+        if (ja < k) gs[t * k + ja] = oka ? silu_f32(c[0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
+        if (jb < k) gs[t * k + jb] = okb ? silu_f32(c[2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
+      } else {  // raw dot products (backward pass)
+        if (ja < k) gs[t * k + ja] = oka ? c[0] : 0.f;
+        if (jb < k) gs[t * k + jb] = okb ? c[2] : 0.f;
+      }
     }
   }
   if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_EXPERT_ID);
@@ -437,8 +444,8 @@ ExpertWs carve(void* ws, int64_t T, int64_t N, int k) {
 }
 
 template <typename T, int NCH>
-void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N, const void* gates, int H, int k,
-                   int64_t P, cudaStream_t stream) {
+void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N, const void* gates, float* gs_out,
+                   int H, int k, int64_t P, cudaStream_t stream) {
   const int chunk = 16;
   const int64_t tasks = (P + chunk - 1) / chunk;
   const int64_t want = (tasks + 7) / 8;
@@ -446,11 +453,11 @@ void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
   expert_scores_kernel<T, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down),
                                                          w.sorted_pair, w.sorted_expert, w.offsets + N,
-                                                         static_cast<const T*>(gates), w.gs, H, k, chunk);
+                                                         static_cast<const T*>(gates), gs_out, H, k, chunk);
 }
 
 template <typename T, typename OutT, int NCH>
-void launch_accum(const void* up, const int64_t* idx, const ExpertWs& w, void* out, int64_t T_, int H, int64_t N, int k,
+void launch_accum(const void* up, const int64_t* idx, const float* gs, void* out, int64_t T_, int H, int64_t N, int k,
                   cudaStream_t stream) {
   constexpr int VEC = Vec16<T>::N;
   const int colblocks = (H + 32 * VEC * NCH - 1) / (32 * VEC * NCH);
@@ -458,23 +465,56 @@ void launch_accum(const void* up, const int64_t* idx, const ExpertWs& w, void* o
   const int64_t want = (tasks + 3) / 4;
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
-  expert_accum_kernel<T, OutT, NCH><<<grid, 128, 0, stream>>>(static_cast<const T*>(up), idx, w.gs,
+  expert_accum_kernel<T, OutT, NCH><<<grid, 128, 0, stream>>>(static_cast<const T*>(up), idx, gs,
                                                               static_cast<OutT*>(out), T_, H, N, k, colblocks);
 }
 
+// Tables that stay resident in the 126 MB L2 are gathered per token (no sort, tensor-core dot
+// products); larger tables take the expert-centric order so each down row leaves HBM once.
+template <typename T> bool use_token_centric(int64_t N, int H) {
+  return sizeof(T) == 2 && (2.0 * static_cast<double>(N) * H * sizeof(T) <= 96.0 * 1024 * 1024);
+}
+
+// counting sort of the (token, slot) pairs by expert id: w.offsets[0..N], w.sorted_pair, w.sorted_expert
+int run_sort(const int64_t* idx, int64_t P, int64_t N, const ExpertWs& w, int32_t* status, cudaStream_t stream) {
+  const int sms = device_sm_count();
+  FMOE_CUDA_TRY(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(N) * 4, stream));
+  {
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_hist_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.counts, w.rank, status);
+    FMOE_LAUNCH_CHECK();
+  }
+  {
+    const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
+    if (ntiles > 16) {
+      scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums);
+      FMOE_LAUNCH_CHECK();
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums, w.offsets);
+    } else {
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, nullptr, w.offsets);
+    }
+    FMOE_LAUNCH_CHECK();
+  }
+  {
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_scatter_kernel<<<grid, 256, 0, stream>>>(idx, w.rank, w.offsets, P, w.sorted_pair, w.sorted_expert);
+    FMOE_LAUNCH_CHECK();
+  }
+  return FMOE_OK;
+}
+
+// per-pair dot products <rows[t], table[e]>: gates != nullptr stores silu(dot) * gate (forward), nullptr the
+// raw dot product.  `sorted` says whether run_sort has filled w for these indices.
 template <typename T>
-int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
-              int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
-              cudaStream_t stream, void* const* between_passes) {
+int run_scores(const void* rows, const void* table, const int64_t* idx, const void* gates, float* out, int64_t T_, int H,
+               int64_t N, int k, const ExpertWs& w, bool sorted, int32_t* status, cudaStream_t stream) {
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
-  const int per_chunk = 32 * VEC;
-  const int need = (H + per_chunk - 1) / per_chunk;
-  // Tables that stay resident in the 126 MB L2 are gathered per token (no sort, tensor-core dot
-  // products); larger tables take the expert-centric order so each down row leaves HBM once.
-  const bool token_centric = sizeof(T) == 2 && (2.0 * static_cast<double>(N) * H * sizeof(T) <= 96.0 * 1024 * 1024);
-  if (token_centric) {
+  const int need = (H + 32 * VEC - 1) / (32 * VEC);
+  if (use_token_centric<T>(N, H)) {
     if constexpr (sizeof(T) == 2) {
       const int64_t want = (T_ * ((k + 15) / 16) + 3) / 4;
       const int64_t cap = static_cast<int64_t>(sms) * 16;
@@ -483,56 +523,384 @@ int run_typed(const void* x, const void* down, const void* up, const int64_t* id
       const int smem = 4 * xs_stride * 16;
       auto kern = expert_scores_mma_kernel<T, 8>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down), idx,
-                                        static_cast<const T*>(gates), w.gs, T_, H, N, k, xs_stride, status);
+      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
+                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status);
       FMOE_LAUNCH_CHECK();
     }
-  } else {
-    FMOE_CUDA_TRY(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(N) * 4, stream));
-    {
-      const int64_t want = (P + 255) / 256;
-      const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
-      expert_hist_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.counts, w.rank, status);
-      FMOE_LAUNCH_CHECK();
-    }
-    {
-      const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
-      if (ntiles > 16) {
-        scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums);
-        FMOE_LAUNCH_CHECK();
-        scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, w.tile_sums, w.offsets);
-      } else {
-        scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.counts, N, nullptr, w.offsets);
-      }
-      FMOE_LAUNCH_CHECK();
-    }
-    {
-      const int64_t want = (P + 255) / 256;
-      const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
-      expert_scatter_kernel<<<grid, 256, 0, stream>>>(idx, w.rank, w.offsets, P, w.sorted_pair, w.sorted_expert);
-      FMOE_LAUNCH_CHECK();
-    }
-    if (need <= 1) launch_scores<T, 1>(x, down, w, N, gates, H, k, P, stream);
-    else if (need <= 2) launch_scores<T, 2>(x, down, w, N, gates, H, k, P, stream);
-    else if (need <= 4) launch_scores<T, 4>(x, down, w, N, gates, H, k, P, stream);
-    else if (need <= 8) launch_scores<T, 8>(x, down, w, N, gates, H, k, P, stream);
-    else launch_scores<T, 0>(x, down, w, N, gates, H, k, P, stream);
-    FMOE_LAUNCH_CHECK();
+    return FMOE_OK;
   }
-  if (between_passes != nullptr)
-    for (int i = 0; i < 2; ++i)
-      if (between_passes[i] != nullptr) FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(between_passes[i]), stream));
+  if (!sorted) {
+    const int rc = run_sort(idx, P, N, w, status, stream);
+    if (rc != FMOE_OK) return rc;
+  }
+  if (need <= 1) launch_scores<T, 1>(rows, table, w, N, gates, out, H, k, P, stream);
+  else if (need <= 2) launch_scores<T, 2>(rows, table, w, N, gates, out, H, k, P, stream);
+  else if (need <= 4) launch_scores<T, 4>(rows, table, w, N, gates, out, H, k, P, stream);
+  else if (need <= 8) launch_scores<T, 8>(rows, table, w, N, gates, out, H, k, P, stream);
+  else launch_scores<T, 0>(rows, table, w, N, gates, out, H, k, P, stream);
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
 
+// out[t] = sum_j coef[t,j] * table[idx[t,j]] (float32 accumulation, one rounding)
+template <typename T>
+int run_accum(const void* table, const int64_t* idx, const float* coef, void* out, int out_f32, int64_t T_, int H,
+              int64_t N, int k, cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  const int need = (H + 32 * VEC - 1) / (32 * VEC);
 #define FMOE_ACCUM(NCH_)                                                                       \
   do {                                                                                         \
-    if (out_f32) launch_accum<T, float, NCH_>(up, idx, w, out, T_, H, N, k, stream);           \
-    else launch_accum<T, T, NCH_>(up, idx, w, out, T_, H, N, k, stream);                       \
+    if (out_f32) launch_accum<T, float, NCH_>(table, idx, coef, out, T_, H, N, k, stream);     \
+    else launch_accum<T, T, NCH_>(table, idx, coef, out, T_, H, N, k, stream);                 \
   } while (0)
   // narrow column blocks: more warps per token, i.e. more gathers in flight
   if (need <= 1) FMOE_ACCUM(1);
   else FMOE_ACCUM(2);
 #undef FMOE_ACCUM
   FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+template <typename T>
+int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
+              int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
+              cudaStream_t stream, void* const* between_passes) {
+  int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream);
+  if (rc != FMOE_OK) return rc;
+  if (between_passes != nullptr)
+    for (int i = 0; i < 2; ++i)
+      if (between_passes[i] != nullptr) FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(between_passes[i]), stream));
+  return run_accum<T>(up, idx, w.gs, out, out_f32, T_, H, N, k, stream);
+}
+
+// ---------------------------------------------------------------- backward
+// Gradients of out[t] = sum_j silu(s_tj) * g_tj * U[e_tj], s_tj = <x[t], D[e_tj]>
+// (flash_moe/ops/triton/flash_expert.py:214-525, host side :653-745):
+//   q_tj  = <dout[t], U[e]>                      dg_tj = q * silu(s)
+//   ds_tj = q * g * silu'(s)                     dx[t] = sum_j ds_tj * D[e]
+//   dD[e] = sum_{pairs of e} ds * x[t]           dU[e] = sum_{pairs of e} silu(s) * g * dout[t]
+// s is recomputed (nothing but the forward's inputs is saved).  All sums are float32 in a fixed order with one
+// rounding on store: no atomics (the reference scatters with atomics), run-to-run deterministic.
+constexpr int kBwdChunk = 64;  // sorted pairs per warp task of the table-gradient pass
+
+// The forward's counting sort orders the pairs of one expert by atomic arrival, which is fine for per-pair
+// results but would make the order of the gradient sums vary from run to run.  The backward therefore sorts
+// (expert id, pair id) with a stable radix sort (CUB, from the CUDA toolkit headers): pairs of one expert end up
+// in ascending pair id, skipped ids (key N) at the end.
+__global__ void expert_sort_keys_kernel(const int64_t* __restrict__ idx, int64_t P, int64_t N,
+                                        unsigned* __restrict__ keys, int* __restrict__ vals, int* __restrict__ counts,
+                                        int32_t* status) {
+  bool bad = false;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < P;
+       p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = idx[p];
+    const bool valid = e >= 0 && e < N;
+    bad |= !valid;
+    keys[p] = valid ? static_cast<unsigned>(e) : static_cast<unsigned>(N);
+    vals[p] = static_cast<int>(p);
+    if (valid) atomicAdd(&counts[e], 1);  // integer counts: the result does not depend on the order
+  }
+  if (bad && status != nullptr) atomicOr(status, FMOE_STATUS_BAD_EXPERT_ID);
+}
+
+int key_bits(int64_t N) {
+  int b = 1;
+  while ((int64_t{1} << b) <= N) ++b;  // keys run from 0 to N inclusive
+  return b;
+}
+
+size_t stable_sort_temp_bytes(int64_t P, int64_t N) {
+  size_t bytes = 0;
+  const cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const unsigned*>(nullptr),
+                                                        static_cast<unsigned*>(nullptr), static_cast<const int*>(nullptr),
+                                                        static_cast<int*>(nullptr), static_cast<int>(P), 0, key_bits(N));
+  if (e != cudaSuccess) {  // no device to ask (host-only size query): a bound that covers CUB's histograms
+    (void)cudaGetLastError();
+    bytes = static_cast<size_t>(P) * 8 + (size_t{4} << 20);
+  }
+  return bytes;
+}
+
+// in: s (raw <x, D>), q (raw <dout, U>), gates.  out: ds (over s), gs = silu(s) * g (over q), dgates.
+template <typename T>
+__global__ void expert_bwd_pairs_kernel(float* __restrict__ s_ds, float* __restrict__ q_gs, const T* __restrict__ gates,
+                                        const int64_t* __restrict__ idx, int64_t N, T* __restrict__ dgates, int64_t P) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < P;
+       p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = idx[p];
+    if (e < 0 || e >= N) {  // a skipped pair contributes nothing and receives no gradient
+      s_ds[p] = 0.f;
+      q_gs[p] = 0.f;
+      dgates[p] = from_f32<T>(0.f);
+      continue;
+    }
+    const float s = s_ds[p], q = q_gs[p], g = to_f32<T>(gates[p]);
+    const float sig = __fdividef(1.0f, 1.0f + __expf(-s));
+    const float act = s * sig;
+    s_ds[p] = q * g * (sig * (1.0f + s * (1.0f - sig)));
+    q_gs[p] = act * g;
+    dgates[p] = from_f32<T>(q * act);
+  }
+}
+
+// One warp per (chunk of kBwdChunk sorted pairs, block of 32*VEC*NCH columns).  The warp walks its pairs in sorted
+// order with the running sums of the current expert's two gradient rows in registers.  A row whose pairs all lie
+// inside the chunk is stored directly; otherwise the partial sum goes to `partial` (slot 0: the expert began in an
+// earlier chunk, slot 1: it began here and continues) and expert_bwd_finish_kernel adds the pieces in chunk order.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(128) expert_bwd_tables_kernel(
+    const T* __restrict__ x, const T* __restrict__ dout, const float* __restrict__ ds, const float* __restrict__ gs,
+    const int* __restrict__ sorted_pair, const int* __restrict__ sorted_expert, const int* __restrict__ offsets,
+    int64_t N, T* __restrict__ ddown, T* __restrict__ dup, float* __restrict__ partial_d, float* __restrict__ partial_u,
+    int H, int k, int colblocks) {
+  constexpr int VEC = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int total = offsets[N];
+  const int64_t nchunks = (total + kBwdChunk - 1) / kBwdChunk;
+  for (int64_t task = warp_global; task < nchunks * colblocks; task += warps_total) {
+    const int64_t chunk = task / colblocks;
+    const int cb = static_cast<int>(task - chunk * colblocks);
+    const int col0 = cb * (32 * VEC * NCH);
+    const int pos0 = static_cast<int>(chunk * kBwdChunk);
+    const int pos1 = min(pos0 + kBwdChunk, total);
+    bool in[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) in[c] = col0 + (c * 32 + lane) * VEC < H;
+    float ad[NCH][VEC], au[NCH][VEC];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ad[c][i] = au[c][i] = 0.f;
+
+    int cur_e = sorted_expert[pos0];
+    bool began_earlier = offsets[cur_e] < pos0;
+    // flush the running sums of expert e: final row, or a partial sum for the finishing pass
+    auto flush = [&](int e, bool partial, int slot) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = col0 + (c * 32 + lane) * VEC;
+        if (!in[c]) continue;
+        if (partial) {
+          float* pd = partial_d + (chunk * 2 + slot) * H + col;
+          float* pu = partial_u + (chunk * 2 + slot) * H + col;
+#pragma unroll
+          for (int i = 0; i < VEC; i += 4) {
+            *reinterpret_cast<float4*>(pd + i) = make_float4(ad[c][i], ad[c][i + 1], ad[c][i + 2], ad[c][i + 3]);
+            *reinterpret_cast<float4*>(pu + i) = make_float4(au[c][i], au[c][i + 1], au[c][i + 2], au[c][i + 3]);
+          }
+        } else {
+          *reinterpret_cast<uint4*>(ddown + static_cast<int64_t>(e) * H + col) = pack16<T>(ad[c]);
+          *reinterpret_cast<uint4*>(dup + static_cast<int64_t>(e) * H + col) = pack16<T>(au[c]);
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) ad[c][i] = au[c][i] = 0.f;
+      }
+    };
+
+    uint4 xn[NCH], on[NCH];
+    int p_next = sorted_pair[pos0];
+    {
+      const int64_t t = p_next / k;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = col0 + (c * 32 + lane) * VEC;
+        xn[c] = in[c] ? ldg16(x + t * H + col) : make_uint4(0, 0, 0, 0);
+        on[c] = in[c] ? ldg16(dout + t * H + col) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    for (int pos = pos0; pos < pos1; ++pos) {
+      const int p = p_next;
+      const int e = sorted_expert[pos];
+      uint4 xq[NCH], oq[NCH];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        xq[c] = xn[c];
+        oq[c] = on[c];
+      }
+      if (pos + 1 < pos1) {  // issue the next pair's row gathers before this pair's math
+        p_next = sorted_pair[pos + 1];
+        const int64_t t = p_next / k;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int col = col0 + (c * 32 + lane) * VEC;
+          xn[c] = in[c] ? ldg16(x + t * H + col) : make_uint4(0, 0, 0, 0);
+          on[c] = in[c] ? ldg16(dout + t * H + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (e != cur_e) {  // warp-uniform: cur_e ends inside this chunk
+        flush(cur_e, began_earlier, 0);
+        cur_e = e;
+        began_earlier = false;
+      }
+      const float wd = ds[p], wu = gs[p];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        float xf[VEC], of[VEC];
+        unpack16<T>(xq[c], xf);
+        unpack16<T>(oq[c], of);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          ad[c][i] = fmaf(wd, xf[i], ad[c][i]);
+          au[c][i] = fmaf(wu, of[i], au[c][i]);
+        }
+      }
+    }
+    const bool continues = offsets[cur_e + 1] > pos1;
+    flush(cur_e, began_earlier || continues, began_earlier ? 0 : 1);
+  }
+}
+
+// One CTA per expert: rows of experts without pairs are zeroed, rows of experts whose pairs span several chunks are
+// the sum of their partial rows in chunk order; rows stored directly by the pass above are left alone.
+template <typename T>
+__global__ void __launch_bounds__(256) expert_bwd_finish_kernel(const int* __restrict__ offsets, int64_t N,
+                                                                const float* __restrict__ partial_d,
+                                                                const float* __restrict__ partial_u,
+                                                                T* __restrict__ ddown, T* __restrict__ dup, int H) {
+  constexpr int VEC = Vec16<T>::N;
+  for (int64_t e = blockIdx.x; e < N; e += gridDim.x) {
+    const int b = offsets[e], en = offsets[e + 1];
+    T* rd = ddown + e * H;
+    T* ru = dup + e * H;
+    if (b == en) {
+      for (int col = threadIdx.x * VEC; col < H; col += blockDim.x * VEC) {
+        *reinterpret_cast<uint4*>(rd + col) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(ru + col) = make_uint4(0, 0, 0, 0);
+      }
+      continue;
+    }
+    const int c0 = b / kBwdChunk, c1 = (en - 1) / kBwdChunk;
+    if (c0 == c1) continue;
+    for (int col = threadIdx.x * VEC; col < H; col += blockDim.x * VEC) {
+      float sd[VEC], su[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) sd[i] = su[i] = 0.f;
+      for (int c = c0; c <= c1; ++c) {
+        const int64_t row = static_cast<int64_t>(c) * 2 + (c == c0 ? 1 : 0);
+        const float* pd = partial_d + row * H + col;
+        const float* pu = partial_u + row * H + col;
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(pd + i);
+          const float4 u = *reinterpret_cast<const float4*>(pu + i);
+          sd[i] += a.x; sd[i + 1] += a.y; sd[i + 2] += a.z; sd[i + 3] += a.w;
+          su[i] += u.x; su[i + 1] += u.y; su[i + 2] += u.z; su[i + 3] += u.w;
+        }
+      }
+      *reinterpret_cast<uint4*>(rd + col) = pack16<T>(sd);
+      *reinterpret_cast<uint4*>(ru + col) = pack16<T>(su);
+    }
+  }
+}
+
+struct ExpertBwdWs {
+  ExpertWs fwd;  // sort arrays; fwd.gs holds s, then ds
+  float* q;      // <dout, U>, then silu(s) * g
+  unsigned* keys_in;
+  int* vals_in;
+  void* sort_temp;
+  size_t sort_temp_bytes;
+  float* partial_d;
+  float* partial_u;
+  size_t bytes;
+};
+
+ExpertBwdWs carve_bwd(void* ws, int64_t T, int H, int64_t N, int k) {
+  ExpertBwdWs w;
+  w.fwd = carve(ws, T, N, k);
+  size_t off = w.fwd.bytes;
+  auto take = [&](size_t bytes) {
+    void* p = ws ? static_cast<char*>(ws) + off : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  };
+  const int64_t P = T * k;
+  const int64_t nchunks = (P + kBwdChunk - 1) / kBwdChunk;
+  w.q = static_cast<float*>(take(static_cast<size_t>(P) * 4));
+  w.keys_in = static_cast<unsigned*>(take(static_cast<size_t>(P) * 4));
+  w.vals_in = static_cast<int*>(take(static_cast<size_t>(P) * 4));
+  w.sort_temp_bytes = stable_sort_temp_bytes(P, N);
+  w.sort_temp = take(w.sort_temp_bytes);
+  w.partial_d = static_cast<float*>(take(static_cast<size_t>(nchunks) * 2 * H * 4));
+  w.partial_u = static_cast<float*>(take(static_cast<size_t>(nchunks) * 2 * H * 4));
+  w.bytes = off;
+  return w;
+}
+
+template <typename T, int NCH>
+void launch_bwd_tables(const void* x, const void* dout, const ExpertBwdWs& w, int64_t N, void* ddown, void* dup, int H,
+                       int k, int64_t P, cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  const int colblocks = (H + 32 * VEC * NCH - 1) / (32 * VEC * NCH);
+  const int64_t tasks = ((P + kBwdChunk - 1) / kBwdChunk) * colblocks;
+  const int64_t want = (tasks + 3) / 4;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
+  const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+  expert_bwd_tables_kernel<T, NCH><<<grid, 128, 0, stream>>>(
+      static_cast<const T*>(x), static_cast<const T*>(dout), w.fwd.gs, w.q, w.fwd.sorted_pair, w.fwd.sorted_expert,
+      w.fwd.offsets, N, static_cast<T*>(ddown), static_cast<T*>(dup), w.partial_d, w.partial_u, H, k, colblocks);
+}
+
+template <typename T>
+int run_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* idx,
+                 const void* gates, void* dx, void* ddown, void* dup, void* dgates, int64_t T_, int H, int64_t N, int k,
+                 const ExpertBwdWs& w, int32_t* status, cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  const int64_t P = T_ * k;
+  const int sms = device_sm_count();
+  int rc;
+  {  // stable sort of the pairs by expert id + segment offsets
+    FMOE_CUDA_TRY(cudaMemsetAsync(w.fwd.counts, 0, static_cast<size_t>(N) * 4, stream));
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_sort_keys_kernel<<<grid, 256, 0, stream>>>(idx, P, N, w.keys_in, w.vals_in, w.fwd.counts, status);
+    FMOE_LAUNCH_CHECK();
+    const int ntiles = static_cast<int>((N + kScanTile - 1) / kScanTile);
+    if (ntiles > 16) {
+      scan_tile_sums_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.fwd.counts, N, w.fwd.tile_sums);
+      FMOE_LAUNCH_CHECK();
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.fwd.counts, N, w.fwd.tile_sums, w.fwd.offsets);
+    } else {
+      scan_apply_kernel<<<ntiles, kScanThreads, 0, stream>>>(w.fwd.counts, N, nullptr, w.fwd.offsets);
+    }
+    FMOE_LAUNCH_CHECK();
+    size_t need = 0;
+    FMOE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, w.keys_in,
+                                                  reinterpret_cast<unsigned*>(w.fwd.sorted_expert), w.vals_in,
+                                                  w.fwd.sorted_pair, static_cast<int>(P), 0, key_bits(N), stream));
+    if (need > w.sort_temp_bytes) return FMOE_ERR_WORKSPACE;
+    size_t have = w.sort_temp_bytes;
+    FMOE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(w.sort_temp, have, w.keys_in,
+                                                  reinterpret_cast<unsigned*>(w.fwd.sorted_expert), w.vals_in,
+                                                  w.fwd.sorted_pair, static_cast<int>(P), 0, key_bits(N), stream));
+  }
+  rc = run_scores<T>(x, down, idx, nullptr, w.fwd.gs, T_, H, N, k, w.fwd, true, status, stream);
+  if (rc != FMOE_OK) return rc;
+  rc = run_scores<T>(dout, up, idx, nullptr, w.q, T_, H, N, k, w.fwd, true, status, stream);
+  if (rc != FMOE_OK) return rc;
+  {
+    const int64_t want = (P + 255) / 256;
+    const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
+    expert_bwd_pairs_kernel<T><<<grid, 256, 0, stream>>>(w.fwd.gs, w.q, static_cast<const T*>(gates), idx, N,
+                                                        static_cast<T*>(dgates), P);
+    FMOE_LAUNCH_CHECK();
+  }
+  rc = run_accum<T>(down, idx, w.fwd.gs, dx, sizeof(T) == 4 ? 1 : 0, T_, H, N, k, stream);
+  if (rc != FMOE_OK) return rc;
+  const int need = (H + 32 * VEC - 1) / (32 * VEC);
+  if (need <= 1) launch_bwd_tables<T, 1>(x, dout, w, N, ddown, dup, H, k, P, stream);
+  else if (need <= 2) launch_bwd_tables<T, 2>(x, dout, w, N, ddown, dup, H, k, P, stream);
+  else launch_bwd_tables<T, 4>(x, dout, w, N, ddown, dup, H, k, P, stream);
+  FMOE_LAUNCH_CHECK();
+  {
+    const int64_t cap = static_cast<int64_t>(sms) * 16;
+    const int grid = static_cast<int>(N < cap ? N : cap);
+    expert_bwd_finish_kernel<T><<<grid, 256, 0, stream>>>(w.fwd.offsets, N, w.partial_d, w.partial_u,
+                                                          static_cast<T*>(ddown), static_cast<T*>(dup), H);
+    FMOE_LAUNCH_CHECK();
+  }
   return FMOE_OK;
 }
 
@@ -572,6 +940,46 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
     case FMOE_DTYPE_F16:
       return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
                                       between_passes);
+    default:
+      return FMOE_ERR_BAD_ARG;
+  }
+}
+
+size_t expert_backward_workspace_bytes(int64_t T, int H, int64_t N, int k) {
+  if (T < 0 || N < 0 || k < 0 || H <= 0) return 0;
+  return carve_bwd(nullptr, T, H, N, k).bytes;
+}
+
+int launch_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
+                           const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype, int64_t T,
+                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+  if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
+  if (dx == nullptr || ddown == nullptr || dup == nullptr) return FMOE_ERR_BAD_ARG;
+  if (N > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
+  const int vec = 16 / dtype_size(dtype);
+  if (H % vec != 0) return FMOE_ERR_ALIGNMENT;
+  if (!aligned16(dx) || !aligned16(ddown) || !aligned16(dup)) return FMOE_ERR_ALIGNMENT;
+  const size_t table_bytes = static_cast<size_t>(N) * H * dtype_size(dtype);
+  if (T == 0 || k == 0) {  // no pairs: every gradient is zero
+    FMOE_CUDA_TRY(cudaMemsetAsync(ddown, 0, table_bytes, stream));
+    FMOE_CUDA_TRY(cudaMemsetAsync(dup, 0, table_bytes, stream));
+    if (T > 0) FMOE_CUDA_TRY(cudaMemsetAsync(dx, 0, static_cast<size_t>(T) * H * dtype_size(dtype), stream));
+    return FMOE_OK;
+  }
+  if (dout == nullptr || x == nullptr || down == nullptr || up == nullptr || indices == nullptr || gates == nullptr ||
+      dgates == nullptr)
+    return FMOE_ERR_BAD_ARG;
+  if (!aligned16(dout) || !aligned16(x) || !aligned16(down) || !aligned16(up)) return FMOE_ERR_ALIGNMENT;
+  const ExpertBwdWs w = carve_bwd(ws, T, H, N, k);
+  if (ws == nullptr || ws_bytes < w.bytes) return FMOE_ERR_WORKSPACE;
+  switch (dtype) {
+    case FMOE_DTYPE_F32:
+      return run_backward<float>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream);
+    case FMOE_DTYPE_BF16:
+      return run_backward<__nv_bfloat16>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status,
+                                         stream);
+    case FMOE_DTYPE_F16:
+      return run_backward<__half>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream);
     default:
       return FMOE_ERR_BAD_ARG;
   }

@@ -14,6 +14,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import _lib
 
@@ -132,6 +133,27 @@ class FlashMoE(nn.Module):
             n += 2  # batch statistics pass + finalize
         return n
 
+    def _forward_differentiable(self, hidden_states, return_routing=False):
+        """The layer as a chain of autograd nodes (same order of operations as the reference module)."""
+        from ..ops.flash_expert import flash_expert_func
+        from ..ops.flash_mlp import flash_mlp_func
+        from ..ops.flash_router import flash_router_func
+
+        bsz, seq_len, _ = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_size)
+        router_logits = self.router_gate(self.router_norm(x))
+        router_logits = router_logits.view(bsz * seq_len, 2, -1).transpose(0, 1)
+        log_probs = F.log_softmax(router_logits, dim=-1)
+        scores, indices = flash_router_func(log_probs, self.num_keys, self.top_k)
+        gates = torch.exp(scores)
+        if self.norm_topk_prob:
+            gates = gates / gates.sum(dim=-1, keepdim=True)
+        experts = flash_expert_func(x, self.down_embed.weight, self.up_embed.weight, indices, gates)
+        shared = flash_mlp_func(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        if return_routing:
+            self.last_indices, self.last_gates = indices, gates.detach()
+        return (shared + experts).view(bsz, seq_len, -1), router_logits
+
     def forward(
         self,
         hidden_states: torch.Tensor,
@@ -140,7 +162,12 @@ class FlashMoE(nn.Module):
         bn_sync_group=None,
         **kwargs,
     ) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(y[B,S,H], router_logits[2, B*S, num_keys]) like the reference; forward only.
+        """(y[B,S,H], router_logits[2, B*S, num_keys]) like the reference.
+
+        With autograd off (``torch.no_grad()`` / inference mode, or nothing that requires grad) one fused library
+        call runs the whole layer.  When a graph is being recorded the layer is composed of the three
+        differentiable ops with torch's batch-norm, linear and log-softmax around them, exactly like the
+        reference's forward (flash_moe/modules/flash_moe.py:55-105), so ``backward()`` works.
 
         ``bn_sync_group``: a torch.distributed process group over which the tokens are sharded.  In
         training mode the router batch-norm then uses the statistics of the whole (global) batch: the
@@ -151,6 +178,10 @@ class FlashMoE(nn.Module):
         """
         bsz, seq_len, _ = hidden_states.shape
         dev = _lib.require_cuda(hidden_states)
+        if torch.is_grad_enabled() and (hidden_states.requires_grad or any(p.requires_grad for p in self.parameters())):
+            if bn_sync_group is not None or stage_timer is not None:
+                raise _lib.FmoeError("bn_sync_group and stage_timer belong to the fused path: call under torch.no_grad()")
+            return self._forward_differentiable(hidden_states, return_routing)
         x = hidden_states.reshape(-1, self.hidden_size)
         if not x.is_contiguous():
             x = x.contiguous()

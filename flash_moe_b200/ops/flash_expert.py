@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from .utils import ForwardOnly, contiguous
+from .utils import contiguous
 
 
 def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, out_dtype=None):
@@ -39,10 +39,43 @@ def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_we
     return out
 
 
-class FlashExpertFunc(ForwardOnly):
+def _expert_backward(dout, hidden_states, down_weights, up_weights, indices, routing_weights):
+    """(dx, ddown, dup, dgates) of the expert sum (flash_moe/ops/triton/flash_expert.py:653-745)."""
+    dev = _lib.require_cuda(dout, hidden_states, down_weights, up_weights, indices, routing_weights)
+    do, x, d, u, idx, g = (contiguous(t) for t in (dout, hidden_states, down_weights, up_weights, indices, routing_weights))
+    T, H = x.shape
+    N, k = d.shape[0], idx.shape[1]
+    if do.dtype != x.dtype:
+        do = do.to(x.dtype)
+    if idx.dtype != torch.int64:
+        idx = idx.to(torch.int64)
+    if g.dtype != x.dtype:
+        g = g.to(x.dtype)
+    dx, dd, du, dg = torch.empty_like(x), torch.empty_like(d), torch.empty_like(u), torch.empty_like(g)
+    L = _lib.lib()
+    ws_bytes = L.fmoe_expert_backward_workspace_bytes(T, H, N, k)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.fmoe_expert_backward(
+            do.data_ptr(), x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), dx.data_ptr(),
+            dd.data_ptr(), du.data_ptr(), dg.data_ptr(), _lib.dtype_code(x), T, H, N, k, ws.data_ptr(), ws_bytes,
+            _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+        )
+    _lib.check(rc, "fmoe_expert_backward")
+    return dx, dd, du, dg
+
+
+class FlashExpertFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden_states, down_weights, up_weights, indices, routing_weights):
+        ctx.save_for_backward(hidden_states, down_weights, up_weights, indices, routing_weights)
         return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights)
+
+    @staticmethod
+    def backward(ctx, dexperts_states):
+        x, d, u, idx, g = ctx.saved_tensors
+        dx, dd, du, dg = _expert_backward(dexperts_states, x, d, u, idx, g)
+        return dx, dd, du, None, dg.to(g.dtype)
 
 
 def flash_expert_func(hidden_states, down_weights, up_weights, indices, routing_weights):

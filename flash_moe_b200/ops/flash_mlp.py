@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from .utils import ForwardOnly, contiguous
+from .utils import contiguous
 
 
 def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None):
@@ -37,10 +37,46 @@ def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None):
     return out.view(*lead, H)
 
 
-class FlashMLPFunc(ForwardOnly):
+def swiglu_backward(dh, a, b, want_h=False):
+    """(da, db[, h]) for h = silu(a) * b (flash_moe/ops/triton/flash_mlp.py:52-102,:125-147)."""
+    dev = _lib.require_cuda(dh, a, b)
+    dh, a, b = (contiguous(t) for t in (dh, a, b))
+    if not (dh.shape == a.shape == b.shape and dh.dtype == a.dtype == b.dtype):
+        raise _lib.FmoeError("dh, a and b must share shape and dtype")
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    h = torch.empty_like(a) if want_h else None
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fmoe_swiglu_backward(dh.data_ptr(), a.data_ptr(), b.data_ptr(), da.data_ptr(), db.data_ptr(),
+                                             _lib.ptr(h), _lib.dtype_code(a), a.numel(), _lib.current_stream_ptr(dev))
+    _lib.check(rc, "fmoe_swiglu_backward")
+    return (da, db, h) if want_h else (da, db)
+
+
+class FlashMLPFunc(torch.autograd.Function):
+    """Forward: the fused kernels.  Backward: like the reference (flash_mlp.py:150-181) the contractions are plain
+    library GEMMs (torch.matmul); the two pre-activations are recomputed instead of saved, the SwiGLU derivative
+    is this library's kernel."""
+
     @staticmethod
     def forward(ctx, x, gate_weight, up_weight, down_weight):
+        ctx.save_for_backward(x, gate_weight, up_weight, down_weight)
         return _mlp_forward(x, gate_weight, up_weight, down_weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wg, wu, wd = ctx.saved_tensors
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        dy2 = dy.reshape(-1, H).to(x2.dtype)
+        a = torch.matmul(x2, wg.t())
+        b = torch.matmul(x2, wu.t())
+        dh = torch.matmul(dy2, wd)
+        da, db, h = swiglu_backward(dh, a, b, want_h=True)
+        dwd = torch.matmul(dy2.t(), h)
+        dwg = torch.matmul(da.t(), x2)
+        dwu = torch.matmul(db.t(), x2)
+        dx = torch.addmm(torch.matmul(da, wg), db, wu)
+        return dx.view_as(x), dwg, dwu, dwd
 
 
 def flash_mlp_func(x, gate_weight, up_weight, down_weight):

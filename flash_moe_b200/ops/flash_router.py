@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from .utils import ForwardOnly, contiguous
+from .utils import contiguous
 
 
 def _router_forward(router_logits: torch.Tensor, num_expert_keys: int, num_experts_per_tok: int, want_gates=False,
@@ -35,12 +35,36 @@ def _router_forward(router_logits: torch.Tensor, num_expert_keys: int, num_exper
     return (scores, indices, gates) if want_gates else (scores, indices)
 
 
-class FlashRouterFunc(ForwardOnly):
+def _router_backward(dscores, indices, num_expert_keys):
+    """dlog_probs[2,T,nk] of the selected sums (flash_moe/ops/triton/flash_router.py:316-345)."""
+    dev = _lib.require_cuda(dscores, indices)
+    ds, idx = contiguous(dscores), contiguous(indices)
+    T, k = ds.shape
+    out = torch.empty((2, T, num_expert_keys), device=dev, dtype=ds.dtype)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fmoe_router_topk_backward(ds.data_ptr(), idx.data_ptr(), _lib.dtype_code(ds), T, num_expert_keys, k,
+                                                  out.data_ptr(), _lib.current_stream_ptr(dev))
+    _lib.check(rc, "fmoe_router_topk_backward")
+    return out
+
+
+class FlashRouterFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, router_logits, num_expert_keys, num_experts_per_tok):
         scores, indices = _router_forward(router_logits, num_expert_keys, num_experts_per_tok)
         ctx.mark_non_differentiable(indices)
+        ctx.save_for_backward(indices)
+        ctx.num_expert_keys = num_expert_keys
+        ctx.in_keys = router_logits.size(2)
         return scores, indices
+
+    @staticmethod
+    def backward(ctx, dscores, dindices):
+        (indices,) = ctx.saved_tensors
+        d = _router_backward(dscores, indices, ctx.num_expert_keys)
+        if ctx.in_keys != ctx.num_expert_keys:  # the forward read only the first num_expert_keys columns
+            d = torch.nn.functional.pad(d, (0, ctx.in_keys - ctx.num_expert_keys))
+        return d, None, None
 
 
 def flash_router_func(router_logits, num_expert_keys, num_experts_per_tok):

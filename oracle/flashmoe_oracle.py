@@ -157,6 +157,107 @@ def mlp_forward_eager(x2d, gate_w, up_w, down_w) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------------------
+# Backward of the three ops (float32 restatements)
+# --------------------------------------------------------------------------------------
+def router_backward(dscores: torch.Tensor, indices: torch.Tensor, num_keys: int) -> torch.Tensor:
+    """``dlog_probs[2,T,nk]``: every selected pair (i, j) passes its score gradient to sub-key i of half 0 and
+    sub-key j of half 1 (flash_moe/ops/triton/flash_router.py:197-249,:316-345).  float32 sums."""
+    T = dscores.shape[0]
+    d = torch.zeros(2, T, num_keys, dtype=torch.float32)
+    ds = dscores.float()
+    d[0].scatter_add_(1, indices // num_keys, ds)
+    d[1].scatter_add_(1, indices % num_keys, ds)
+    return d
+
+
+def expert_backward(dout, x2d, down_table, up_table, indices, gates, chunk: int = 256):
+    """``(dx, ddown, dup, dgates)`` of `expert_forward` in float32.
+
+    Restates flash_moe/ops/triton/flash_expert.py:214-525 (host side :653-745): with s = <x, D[e]>,
+    q = <dout, U[e]>: dgate = q*silu(s), ds = q*gate*silu'(s), dx = sum ds*D[e], dD[e] += ds*x, dU[e] += silu(s)*gate*dout.
+    """
+    T, H = x2d.shape
+    N = down_table.shape[0]
+    dx = torch.empty(T, H)
+    dd = torch.zeros(N, H)
+    du = torch.zeros(N, H)
+    dg = torch.empty(indices.shape, dtype=torch.float32)
+    for t0 in range(0, T, chunk):
+        ids = indices[t0 : t0 + chunk]
+        xs, do = x2d[t0 : t0 + chunk].float(), dout[t0 : t0 + chunk].float()
+        d, u = down_table[ids].float(), up_table[ids].float()
+        g = gates[t0 : t0 + chunk].float()
+        s = torch.einsum("tkh,th->tk", d, xs)
+        q = torch.einsum("tkh,th->tk", u, do)
+        sig = torch.sigmoid(s)
+        act = s * sig
+        ds = q * g * sig * (1 + s * (1 - sig))
+        dg[t0 : t0 + chunk] = q * act
+        dx[t0 : t0 + chunk] = torch.einsum("tk,tkh->th", ds, d)
+        dd.index_add_(0, ids.reshape(-1), (ds.unsqueeze(-1) * xs.unsqueeze(1)).reshape(-1, H))
+        du.index_add_(0, ids.reshape(-1), ((act * g).unsqueeze(-1) * do.unsqueeze(1)).reshape(-1, H))
+    return dx, dd, du, dg
+
+
+def swiglu_backward(dh, a, b):
+    """``(da, db)`` of h = silu(a) * b in float32 (flash_moe/ops/triton/flash_mlp.py:52-102)."""
+    dh, a, b = dh.float(), a.float(), b.float()
+    sig = torch.sigmoid(a)
+    return dh * b * sig * (1 + a * (1 - sig)), dh * a * sig
+
+
+def mlp_backward(dy, x2d, gate_w, up_w, down_w):
+    """``(dx, dgate_w, dup_w, ddown_w)`` of `mlp_forward` in float32: the chain the reference's autograd builds
+    from its matmuls and `TritonSwiGLUFunc` (flash_moe/ops/triton/flash_mlp.py:150-181)."""
+    dy, xs, wg, wu, wd = dy.float(), x2d.float(), gate_w.float(), up_w.float(), down_w.float()
+    a, b = xs @ wg.t(), xs @ wu.t()
+    h = F.silu(a) * b
+    da, db = swiglu_backward(dy @ wd, a, b)
+    return da @ wg + db @ wu, da.t() @ xs, db.t() @ xs, dy.t() @ h
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, log_probs, num_keys, top_k):
+        scores, indices = router_topk(log_probs, num_keys, top_k)
+        ctx.save_for_backward(indices)
+        ctx.num_keys = num_keys
+        ctx.mark_non_differentiable(indices)
+        return scores, indices
+
+    @staticmethod
+    def backward(ctx, dscores, _):
+        (indices,) = ctx.saved_tensors
+        return router_backward(dscores, indices, ctx.num_keys).to(dscores.dtype), None, None
+
+
+class _ExpertFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2d, down_table, up_table, indices, gates):
+        ctx.save_for_backward(x2d, down_table, up_table, indices, gates)
+        return expert_forward(x2d, down_table, up_table, indices, gates).to(x2d.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2d, down_table, up_table, indices, gates = ctx.saved_tensors
+        dx, dd, du, dg = expert_backward(dout, x2d, down_table, up_table, indices, gates)
+        return dx.to(x2d.dtype), dd.to(down_table.dtype), du.to(up_table.dtype), None, dg.to(gates.dtype)
+
+
+class _MlpFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2d, gate_w, up_w, down_w):
+        ctx.save_for_backward(x2d, gate_w, up_w, down_w)
+        return mlp_forward(x2d, gate_w, up_w, down_w).to(x2d.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, gate_w, up_w, down_w = ctx.saved_tensors
+        dx, dg, du, dd = mlp_backward(dy, x2d, gate_w, up_w, down_w)
+        return dx.to(x2d.dtype), dg.to(gate_w.dtype), du.to(up_w.dtype), dd.to(down_w.dtype)
+
+
+# --------------------------------------------------------------------------------------
 # The whole layer
 # --------------------------------------------------------------------------------------
 class OracleFlashMoE(nn.Module):
@@ -205,6 +306,20 @@ class OracleFlashMoE(nn.Module):
         mlp = mlp_forward_eager(x2d, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
         y = (mlp + experts).view(B, S, H)
         return y, logits.view(B * S, 2, self.num_keys).transpose(0, 1)
+
+    def forward_differentiable(self, hidden_states: torch.Tensor):
+        """The forward as a chain of autograd nodes whose three custom ops use the explicit backward
+        restatements above; everything else (batch-norm, linear, log-softmax, exp, add) is torch autograd, as in
+        the reference module (flash_moe/modules/flash_moe.py:55-105)."""
+        B, S, H = hidden_states.shape
+        x2d = hidden_states.reshape(-1, H)
+        logits = self.router_gate(self.router_norm(x2d))
+        halves = logits.view(B * S, 2, -1).transpose(0, 1)
+        scores, indices = _RouterFn.apply(F.log_softmax(halves, dim=-1), self.num_keys, self.top_k)
+        gates = routing_weights(scores, self.norm_topk_prob)
+        experts = _ExpertFn.apply(x2d, self.down_embed.weight, self.up_embed.weight, indices, gates)
+        mlp = _MlpFn.apply(x2d, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        return (mlp + experts).view(B, S, H), halves
 
     def forward_fp32_given_routing(self, hidden_states, indices, gates, round_h_to=None) -> torch.Tensor:
         """float32 evaluation of experts + MLP + add on the stored (possibly bf16) operands for a *given* routing.

@@ -95,6 +95,27 @@ def layer_case(name, H, I, N, k, norm, B, S, dtype, store_inputs, train=False):
     print(name, "y rms", float(y.float().pow(2).mean().sqrt()), "digest", digest[:12])
 
 
+def layer_grad_case(name, H, I, N, k, norm, B, S, train=False):
+    """Gradients of loss = sum(y * w) through the reference's eager module under torch autograd (float32)."""
+    torch.manual_seed(0)
+    mod = FlashMoE_Pytorch(make_cfg(H, I, N, k, norm))
+    mod.train(train)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(B, S, H, generator=g, requires_grad=True)
+    w = torch.randn(B, S, H, generator=g)
+    sd = {k_: v.clone() for k_, v in mod.state_dict().items()}
+    y, _ = mod(x)
+    (y * w).sum().backward()
+    out = {"cfg": np.array([H, I, N, k, int(norm), B, S, int(train)], dtype=np.int64), "x": x.detach().numpy(),
+           "w": w.numpy(), "y": y.detach().numpy(), "grad.x": x.grad.numpy()}
+    for n, p in mod.named_parameters():
+        out["grad." + n] = p.grad.numpy()
+    for n, p in sd.items():
+        out["param." + n] = p.float().numpy()
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print(name, "grad norms", {n: float(p.grad.norm()) for n, p in mod.named_parameters()})
+
+
 def pin_autotuner(kernel):
     if hasattr(kernel, "configs"):
         kernel.configs = kernel.configs[:1]
@@ -159,6 +180,8 @@ if __name__ == "__main__":
     layer_case("eager_mini_fp32_train_norm", 64, 128, 256, 4, True, 2, 16, torch.float32, store_inputs=True, train=True)
     layer_case("eager_mini_bf16", 64, 128, 256, 4, False, 2, 16, torch.bfloat16, store_inputs=True)
     layer_case("eager_c1_fp32", 256, 1024, 1024, 8, False, 1, 256, torch.float32, store_inputs=False)
+    layer_grad_case("eager_mini_fp32_grads", 64, 128, 256, 4, False, 2, 16)
+    layer_grad_case("eager_mini_fp32_grads_norm_train", 64, 128, 256, 4, True, 2, 16, train=True)
     # Triton kernels under the interpreter
     triton_router_case("triton_router_nk16_k4", 16, 16, 4, tied=False)
     triton_router_case("triton_router_nk16_k4_tied", 16, 16, 4, tied=True)
