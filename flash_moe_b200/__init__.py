@@ -1,4 +1,4 @@
-"""flash_moe_b200: the forward hot path of the FlashMoE layer on NVIDIA B200 (sm_100a).
+"""flash_moe_b200: the hot path of the FlashMoE layer (fused forward, backward of its three ops) on NVIDIA B200 (sm_100a).
 
 Python host code over a C-ABI shared library of hand-written CUDA kernels
 (`libfmoe_sm100a.so`, declared in `include/fmoe.h`).  Mirrors the reference's

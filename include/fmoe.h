@@ -1,7 +1,7 @@
 /*
- * fmoe.h - C ABI of libfmoe_sm100a.so: the forward hot path of the FlashMoE layer
- * (product-key router -> fine-grained experts -> shared SwiGLU MLP) as hand-written
- * CUDA kernels for NVIDIA B200 (sm_100a).
+ * fmoe.h - C ABI of libfmoe_sm100a.so: the hot path of the FlashMoE layer
+ * (product-key router -> fine-grained experts -> shared SwiGLU MLP; the fused forward and
+ * the backward of the three ops) as hand-written CUDA kernels for NVIDIA B200 (sm_100a).
  *
  * Conventions
  *   - every data pointer is a DEVICE pointer, row-major and contiguous unless stated;
