@@ -10,5 +10,7 @@ from .modules.flash_moe import FlashMoE, FlashMoEConfig, GraphedFlashMoE, StageT
 from .ops.flash_expert import flash_expert_func, triton_flash_expert_func  # noqa: F401
 from .ops.flash_mlp import flash_mlp_func, triton_flash_mlp_func  # noqa: F401
 from .ops.flash_router import flash_router_func, triton_flash_router_func  # noqa: F401
+from .ops.peer import peer_func, triton_peer_func  # noqa: F401
+from .ops.pkm import pkm_func, triton_pkm_func  # noqa: F401
 
 __version__ = "0.1.0"

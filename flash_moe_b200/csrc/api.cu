@@ -181,6 +181,27 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
                         static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_peer_forward(const void* x, const void* down, const void* up, const void* routing_weights,
+                      const int64_t* indices, void* out, int dtype, int64_t num_tokens, int hidden, int64_t num_experts,
+                      int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_expert_forward(x, down, up, indices, routing_weights, out, dtype, dtype, num_tokens, hidden, num_experts,
+                               top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream), nullptr,
+                               kActGelu);
+}
+
+size_t fmoe_pkm_workspace_bytes(int64_t num_tokens, int top_k) {
+  return (num_tokens < 0 || top_k < 0) ? 0 : static_cast<size_t>(num_tokens) * top_k * 4;
+}
+
+int fmoe_pkm_forward(const void* values, const void* routing_weights, const int64_t* indices, void* out, int dtype,
+                     int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                     size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_weighted_rows(values, routing_weights, indices, out, dtype, num_tokens, hidden, num_experts, top_k,
+                              workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
 int fmoe_router_topk_backward(const void* dscores, const int64_t* indices, int dtype, int64_t num_tokens, int num_keys,
                               int top_k, void* dlog_probs, fmoe_stream_t stream) {
   if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;

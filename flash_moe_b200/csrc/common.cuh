@@ -47,6 +47,10 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
 
 __device__ __forceinline__ float silu_f32(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+// exact (erf) GELU, the activation of the PEER comparison op (flash_moe/ops/triton/peer.py:116-118)
+__device__ __forceinline__ float gelu_f32(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+enum ExpertAct { kActSilu = 0, kActGelu = 1 };
+__device__ __forceinline__ float expert_act(float v, int act) { return act == kActGelu ? gelu_f32(v) : silu_f32(v); }
 
 // ---- 16-byte vectors of T -----------------------------------------------------------------
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
@@ -115,7 +119,12 @@ int launch_router_topk(const void* log_probs, int dtype, int64_t T, int nk, int 
 size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k);
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
-                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr);
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr,
+                          int act = 0);
+// out[t] = sum_j weights[t,j] * values[indices[t,j]] (the PKM comparison op)
+int launch_weighted_rows(const void* values, const void* weights, const int64_t* indices, void* out, int dtype,
+                         int64_t T, int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status,
+                         cudaStream_t stream);
 // between_passes (nullable): two cudaEvent_t handles (each nullable) recorded back to back after the scores pass
 // and before the accumulate pass.
 

@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
                                                            const int* __restrict__ sorted_expert,
                                                            const int* __restrict__ total_ptr,
                                                            const T* __restrict__ gates, float* __restrict__ gs, int H,
-                                                           int k, int chunk) {
+                                                           int k, int chunk, int act) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int R = NCH > 0 ? NCH : 1;
   const int lane = threadIdx.x & 31;
@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
       }
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFull, acc, d);
-      if (lane == 0) gs[p] = gates != nullptr ? silu_f32(acc) * to_f32<T>(gates[p]) : acc;  // nullptr: raw dot product
+      if (lane == 0) gs[p] = gates != nullptr ? expert_act(acc, act) * to_f32<T>(gates[p]) : acc;  // nullptr: raw dot product
     }
   }
 }
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
                                                                const int64_t* __restrict__ idx,
                                                                const T* __restrict__ gates, float* __restrict__ gs,
                                                                int64_t ntok, int H, int64_t N, int k, int xs_stride,
-                                                               int32_t* status) {
+                                                               int32_t* status, int act) {
   extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -305,8 +305,8 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
     }
     if (tq == 0) {
       if (gates != nullptr) {
-        if (ja < k) gs[t * k + ja] = oka ? silu_f32(c[0]) * to_f32<T>(gates[t * k + ja]) : 0.f;
-        if (jb < k) gs[t * k + jb] = okb ? silu_f32(c[2]) * to_f32<T>(gates[t * k + jb]) : 0.f;
+        if (ja < k) gs[t * k + ja] = oka ? expert_act(c[0], act) * to_f32<T>(gates[t * k + ja]) : 0.f;
+        if (jb < k) gs[t * k + jb] = okb ? expert_act(c[2], act) * to_f32<T>(gates[t * k + jb]) : 0.f;
       } else {  // raw dot products (backward pass)
         if (ja < k) gs[t * k + ja] = oka ? c[0] : 0.f;
         if (jb < k) gs[t * k + jb] = okb ? c[2] : 0.f;
@@ -445,7 +445,7 @@ ExpertWs carve(void* ws, int64_t T, int64_t N, int k) {
 
 template <typename T, int NCH>
 void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N, const void* gates, float* gs_out,
-                   int H, int k, int64_t P, cudaStream_t stream) {
+                   int H, int k, int64_t P, cudaStream_t stream, int act) {
   const int chunk = 16;
   const int64_t tasks = (P + chunk - 1) / chunk;
   const int64_t want = (tasks + 7) / 8;
@@ -453,7 +453,7 @@ void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
   expert_scores_kernel<T, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down),
                                                          w.sorted_pair, w.sorted_expert, w.offsets + N,
-                                                         static_cast<const T*>(gates), gs_out, H, k, chunk);
+                                                         static_cast<const T*>(gates), gs_out, H, k, chunk, act);
 }
 
 template <typename T, typename OutT, int NCH>
@@ -509,7 +509,7 @@ int run_sort(const int64_t* idx, int64_t P, int64_t N, const ExpertWs& w, int32_
 // raw dot product.  `sorted` says whether run_sort has filled w for these indices.
 template <typename T>
 int run_scores(const void* rows, const void* table, const int64_t* idx, const void* gates, float* out, int64_t T_, int H,
-               int64_t N, int k, const ExpertWs& w, bool sorted, int32_t* status, cudaStream_t stream) {
+               int64_t N, int k, const ExpertWs& w, bool sorted, int32_t* status, cudaStream_t stream, int act = 0) {
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
@@ -524,7 +524,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       auto kern = expert_scores_mma_kernel<T, 8>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
-                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status);
+                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act);
       FMOE_LAUNCH_CHECK();
     }
     return FMOE_OK;
@@ -533,11 +533,11 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
     const int rc = run_sort(idx, P, N, w, status, stream);
     if (rc != FMOE_OK) return rc;
   }
-  if (need <= 1) launch_scores<T, 1>(rows, table, w, N, gates, out, H, k, P, stream);
-  else if (need <= 2) launch_scores<T, 2>(rows, table, w, N, gates, out, H, k, P, stream);
-  else if (need <= 4) launch_scores<T, 4>(rows, table, w, N, gates, out, H, k, P, stream);
-  else if (need <= 8) launch_scores<T, 8>(rows, table, w, N, gates, out, H, k, P, stream);
-  else launch_scores<T, 0>(rows, table, w, N, gates, out, H, k, P, stream);
+  if (need <= 1) launch_scores<T, 1>(rows, table, w, N, gates, out, H, k, P, stream, act);
+  else if (need <= 2) launch_scores<T, 2>(rows, table, w, N, gates, out, H, k, P, stream, act);
+  else if (need <= 4) launch_scores<T, 4>(rows, table, w, N, gates, out, H, k, P, stream, act);
+  else if (need <= 8) launch_scores<T, 8>(rows, table, w, N, gates, out, H, k, P, stream, act);
+  else launch_scores<T, 0>(rows, table, w, N, gates, out, H, k, P, stream, act);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }
@@ -564,8 +564,8 @@ int run_accum(const void* table, const int64_t* idx, const float* coef, void* ou
 template <typename T>
 int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
               int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
-              cudaStream_t stream, void* const* between_passes) {
-  int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream);
+              cudaStream_t stream, void* const* between_passes, int act) {
+  int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream, act);
   if (rc != FMOE_OK) return rc;
   if (between_passes != nullptr)
     for (int i = 0; i < 2; ++i)
@@ -795,6 +795,25 @@ __global__ void __launch_bounds__(256) expert_bwd_finish_kernel(const int* __res
   }
 }
 
+template <typename T>
+__global__ void weights_to_f32_kernel(const T* __restrict__ w, float* __restrict__ out, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[i] = to_f32<T>(w[i]);
+}
+
+template <typename T>
+int run_weighted_rows(const void* values, const void* weights, const int64_t* idx, void* out, int64_t T_, int H,
+                      int64_t N, int k, float* coef, cudaStream_t stream) {
+  const int64_t P = T_ * k;
+  const int64_t want = (P + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  weights_to_f32_kernel<T><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(static_cast<const T*>(weights),
+                                                                                          coef, P);
+  FMOE_LAUNCH_CHECK();
+  return run_accum<T>(values, idx, coef, out, sizeof(T) == 4 ? 1 : 0, T_, H, N, k, stream);
+}
+
 struct ExpertBwdWs {
   ExpertWs fwd;  // sort arrays; fwd.gs holds s, then ds
   float* q;      // <dout, U>, then silu(s) * g
@@ -914,8 +933,9 @@ size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k) {
 
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
-                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes) {
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes, int act) {
   if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
+  if (act != kActSilu && act != kActGelu) return FMOE_ERR_BAD_ARG;
   if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
   if (T == 0) return FMOE_OK;
   if (x == nullptr || down == nullptr || up == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
@@ -933,13 +953,13 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
   const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
   switch (dtype) {
     case FMOE_DTYPE_F32:
-      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes);
+      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes, act);
     case FMOE_DTYPE_BF16:
       return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes);
+                                      between_passes, act);
     case FMOE_DTYPE_F16:
       return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes);
+                                      between_passes, act);
     default:
       return FMOE_ERR_BAD_ARG;
   }
@@ -982,6 +1002,31 @@ int launch_expert_backward(const void* dout, const void* x, const void* down, co
       return run_backward<__half>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream);
     default:
       return FMOE_ERR_BAD_ARG;
+  }
+}
+
+int launch_weighted_rows(const void* values, const void* weights, const int64_t* indices, void* out, int dtype,
+                         int64_t T, int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status,
+                         cudaStream_t stream) {
+  (void)status;  // ids outside [0, N) contribute nothing (the accumulate pass skips them)
+  if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
+  if (T == 0) return FMOE_OK;
+  if (values == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
+  if (T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
+  if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(values) || !aligned16(out)) return FMOE_ERR_ALIGNMENT;
+  if (k == 0) {
+    FMOE_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(T) * H * dtype_size(dtype), stream));
+    return FMOE_OK;
+  }
+  if (weights == nullptr || indices == nullptr) return FMOE_ERR_BAD_ARG;
+  const size_t need = static_cast<size_t>(T) * k * 4;
+  if (ws == nullptr || ws_bytes < need) return FMOE_ERR_WORKSPACE;
+  float* coef = static_cast<float*>(ws);
+  switch (dtype) {
+    case FMOE_DTYPE_F32: return run_weighted_rows<float>(values, weights, indices, out, T, H, N, k, coef, stream);
+    case FMOE_DTYPE_BF16: return run_weighted_rows<__nv_bfloat16>(values, weights, indices, out, T, H, N, k, coef, stream);
+    case FMOE_DTYPE_F16: return run_weighted_rows<__half>(values, weights, indices, out, T, H, N, k, coef, stream);
+    default: return FMOE_ERR_BAD_ARG;
   }
 }
 

@@ -106,6 +106,23 @@ int fmoe_expert_forward(const void* x, const void* down, const void* up, const i
                         int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * The two retrieval baselines the reference ships beside its layer, on the same gather kernels.
+ * fmoe_peer_forward - triton_peer_func(hidden_states, down_embed, up_embed, routing_weights, indices),
+ *   flash_moe/ops/triton/peer.py:151-255: out[t] = sum_j gelu(<x[t], down[idx]>) * w[t,j] * up[idx] with the exact
+ *   (erf) GELU; workspace as for fmoe_expert_forward (fmoe_expert_workspace_bytes).
+ * fmoe_pkm_forward - triton_pkm_func(values, routing_weights, indices), flash_moe/ops/triton/pkm.py:123-200:
+ *   out[t] = sum_j w[t,j] * values[idx[t,j]]; workspace fmoe_pkm_workspace_bytes.
+ * float32 accumulation, one rounding to `dtype`; ids outside [0, num_experts) are skipped.
+ */
+int fmoe_peer_forward(const void* x, const void* down, const void* up, const void* routing_weights,
+                      const int64_t* indices, void* out, int dtype, int64_t num_tokens, int hidden, int64_t num_experts,
+                      int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+size_t fmoe_pkm_workspace_bytes(int64_t num_tokens, int top_k);
+int fmoe_pkm_forward(const void* values, const void* routing_weights, const int64_t* indices, void* out, int dtype,
+                     int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                     size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+
+/*
  * Backward of the three ops (the reference's autograd Functions).  Gradients have the dtype of their tensors;
  * every sum is formed in float32 in a fixed order and rounded once (the reference scatters with atomics).
  *

@@ -156,6 +156,19 @@ def mlp_forward_eager(x2d, gate_w, up_w, down_w) -> torch.Tensor:
     return F.linear(F.silu(F.linear(x2d, gate_w)) * F.linear(x2d, up_w), down_w)
 
 
+def peer_forward(x2d, down_table, up_table, weights, indices) -> torch.Tensor:
+    """PEER baseline: ``sum_j gelu(<x, D[idx]>) * w * U[idx]`` with the exact (erf) GELU, float32
+    (flash_moe/ops/triton/peer.py:23-148; eager statement tests/test_peer.py:9-24)."""
+    d, u = down_table[indices].float(), up_table[indices].float()
+    s = torch.einsum("tkh,th->tk", d, x2d.float())
+    return torch.einsum("tk,tkh->th", F.gelu(s) * weights.float(), u)
+
+
+def pkm_forward(values, weights, indices) -> torch.Tensor:
+    """PKM baseline: ``sum_j w[t,j] * values[idx[t,j]]`` in float32 (flash_moe/ops/triton/pkm.py:25-120)."""
+    return torch.einsum("tk,tkh->th", weights.float(), values[indices].float())
+
+
 # --------------------------------------------------------------------------------------
 # Backward of the three ops (float32 restatements)
 # --------------------------------------------------------------------------------------

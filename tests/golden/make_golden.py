@@ -173,6 +173,26 @@ def triton_mlp_case(name, T, H, I):
     print(name, "ok")
 
 
+def triton_peer_pkm_case(name, T, H, N, k):
+    import flash_moe.ops.triton.peer as peer
+    import flash_moe.ops.triton.pkm as pkm
+
+    pin_autotuner(peer._peer_fwd_kernel)
+    pin_autotuner(pkm._pkm_fwd_kernel)
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(T, H, generator=g) * 0.5
+    d = torch.randn(N, H, generator=g) * 0.3
+    u = torch.randn(N, H, generator=g) * 0.3
+    idx = torch.randint(0, N, (T, k), generator=g)
+    idx[0, 1] = idx[0, 0]
+    w = torch.softmax(torch.randn(T, k, generator=g), -1)
+    y_peer = peer.triton_peer_func(x, d, u, w, idx)
+    y_pkm = pkm.triton_pkm_func(u, w, idx)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), x=x.numpy(), down=d.numpy(), up=u.numpy(), weights=w.numpy(),
+                        indices=idx.numpy(), y_peer=y_peer.numpy(), y_pkm=y_pkm.numpy())
+    print(name, "ok")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count() or 1)
     # eager module: a mini case stored with all inputs, and benchmark configuration 1 stored as outputs + digest
@@ -189,3 +209,4 @@ if __name__ == "__main__":
     triton_router_case("triton_router_nk128_k16", 2, 128, 16, tied=False)
     triton_expert_case("triton_expert_small", 16, 64, 64, 4)
     triton_mlp_case("triton_mlp_small", 8, 32, 64)
+    triton_peer_pkm_case("triton_peer_pkm_small", 16, 48, 40, 4)

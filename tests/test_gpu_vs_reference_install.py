@@ -123,3 +123,32 @@ def test_layer_against_reference_module_config2(ref_pkg):
     print("config 2: ours vs fp32", err_ours, " rms(ours - reference)/rms", rms_diff)
     assert err_ours < 3e-2
     assert rms_diff < 2e-2
+
+
+def test_peer_and_pkm_against_reference_triton(ref_pkg):
+    sys.path.insert(0, REF_DIR)
+    try:
+        import flash_moe.ops.triton.peer as ref_peer
+        import flash_moe.ops.triton.pkm as ref_pkm
+    finally:
+        sys.path.remove(REF_DIR)
+    from flash_moe_b200.ops.peer import triton_peer_func
+    from flash_moe_b200.ops.pkm import triton_pkm_func
+
+    T, H, N, k = 512, 256, 4096, 16
+    for dtype in (torch.float32, torch.bfloat16):
+        x = (randn((T, H), 1, torch.float32) * 0.5).to(dtype).cuda()
+        down = (randn((N, H), 2, torch.float32) * 0.2).to(dtype).cuda()
+        up = (randn((N, H), 3, torch.float32) * 0.2).to(dtype).cuda()
+        idx = torch.randint(0, N, (T, k), generator=torch.Generator().manual_seed(4)).cuda()
+        w = torch.softmax(randn((T, k), 5, torch.float32), -1).to(dtype).cuda()
+        for ours, theirs, want in (
+            (triton_peer_func(x, down, up, w, idx), ref_peer.triton_peer_func(x, down, up, w, idx),
+             O.peer_forward(x.cpu(), down.cpu(), up.cpu(), w.cpu(), idx.cpu())),
+            (triton_pkm_func(up, w, idx), ref_pkm.triton_pkm_func(up, w, idx), O.pkm_forward(up.cpu(), w.cpu(), idx.cpu())),
+        ):
+            rms = want.pow(2).mean().sqrt()
+            e_ours = float((ours.float().cpu() - want).abs().max() / rms)
+            e_ref = float((theirs.float().cpu() - want).abs().max() / rms)
+            print(dtype, "max|err|/RMS vs fp32: ours", e_ours, "reference", e_ref)
+            assert e_ours <= max(1e-5 if dtype == torch.float32 else 2e-2, 1.05 * e_ref)

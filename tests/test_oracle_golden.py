@@ -99,3 +99,10 @@ def test_mlp_matches_reference_triton_kernel(golden_dir):
     t = {n: torch.from_numpy(z[n]) for n in z.files}
     y = O.mlp_forward(t["x"], t["wg"], t["wu"], t["wd"])
     np.testing.assert_allclose(y.numpy(), z["y"], rtol=1e-5, atol=1e-6)
+
+
+def test_peer_and_pkm_oracles_match_reference_triton_kernels(golden_dir):
+    z = np.load(os.path.join(golden_dir, "triton_peer_pkm_small.npz"))
+    x, d, u, w, idx = (torch.from_numpy(z[n]) for n in ("x", "down", "up", "weights", "indices"))
+    assert torch.allclose(O.peer_forward(x, d, u, w, idx), torch.from_numpy(z["y_peer"]), rtol=1e-4, atol=1e-5)
+    assert torch.allclose(O.pkm_forward(u, w, idx), torch.from_numpy(z["y_pkm"]), rtol=1e-5, atol=1e-6)
