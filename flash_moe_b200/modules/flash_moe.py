@@ -117,13 +117,12 @@ class FlashMoE(nn.Module):
 
     def kernels_per_forward(self) -> int:
         """Kernels of this library launched by one forward (16-bit dtypes): batch-norm apply, router GEMM,
-        top-k (with the log-softmax inside for num_keys <= 1024), experts (2 kernels when the tables fit L2
-        and are gathered per token, 5 with the expert-centric sort), MLP up GEMM, MLP down GEMM."""
+        top-k (with the log-softmax inside for num_keys <= 1024), experts (2 kernels for 16-bit dtypes, which
+        are gathered per token; 5 with the expert-centric sort of float32), MLP up GEMM, MLP down GEMM."""
         n = 1 + 1 + 1 + 1 + 1
         if self.num_keys > 1024:
             n += 1  # separate log-softmax pass
-        table_bytes = 2 * self.num_experts * self.hidden_size * self.down_embed.weight.element_size()
-        if self.down_embed.weight.element_size() == 2 and table_bytes <= 96 * 1024 * 1024:
+        if self.down_embed.weight.element_size() == 2:
             n += 2  # scores (mma) + accumulate
         else:
             n += 5  # histogram, scan, scatter, scores, accumulate

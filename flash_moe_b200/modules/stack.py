@@ -22,6 +22,9 @@ class FlashMoEStack(nn.Module):
                 torch.manual_seed(seeds[i])
             layers.append(FlashMoE(config))
         self.layers = nn.ModuleList(layers)
+        # the layers run one after another on one stream, so they can share one scratch allocation
+        for layer in layers[1:]:
+            layer._workspaces = layers[0]._workspaces
 
     def forward(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, List[torch.Tensor]]:
         """Returns the final hidden states and every layer's router logits."""

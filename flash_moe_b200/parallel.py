@@ -40,9 +40,8 @@ def plan_dispatch(indices: torch.Tensor, gates: torch.Tensor, num_experts: int, 
 
     Returns `(counts, token_ids, local_ids, local_gates)`: `counts[g]` tokens go to rank g;
     `token_ids` lists them destination by destination; `local_ids/local_gates [sum(counts), k]` hold,
-    per sent token, its slots owned by that destination (local expert id, gate); the other slots carry
-    gate 0, so they contribute nothing, and repeat one of the token's own local ids so that padding does
-    not pile up on a single expert row.  Ids outside [0, num_experts) are dropped.
+    per sent token, its slots owned by that destination (local expert id, gate); the other slots are empty:
+    id -1 (which the expert kernels skip) and gate 0.  Ids outside [0, num_experts) are dropped.
     """
     valid = (indices >= 0) & (indices < num_experts)
     dest = torch.where(valid, indices % world, torch.full_like(indices, -1))
@@ -54,8 +53,7 @@ def plan_dispatch(indices: torch.Tensor, gates: torch.Tensor, num_experts: int, 
         tok = m.any(dim=1).nonzero(as_tuple=True)[0]
         counts.append(int(tok.numel()))
         tok_l.append(tok)
-        own = torch.where(m, local, torch.full_like(local, -1))[tok]
-        id_l.append(torch.where(own >= 0, own, own.max(dim=1, keepdim=True).values))
+        id_l.append(torch.where(m, local, torch.full_like(local, -1))[tok])
         gate_l.append(torch.where(m, gates, zero_g)[tok])
     return counts, torch.cat(tok_l), torch.cat(id_l), torch.cat(gate_l)
 

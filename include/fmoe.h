@@ -97,7 +97,8 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
  *   flash_moe/ops/triton/flash_expert.py:831-836 (forward :580-649, preprocessing :528-577,
  *   kernels :13-211).
  * x [T, H], down/up [N, H], gates [T, k] of `dtype`; indices [T, k] int64 (duplicates inside a
- * token accumulate; ids outside [0, N) are skipped and flagged in *status).
+ * token accumulate; -1 marks an empty slot and is skipped silently; other ids outside [0, N) are
+ * skipped and flagged in *status).
  * out [T, H] of `out_dtype`: `dtype` (one rounding of the fp32 sum) or FMOE_DTYPE_F32.
  */
 size_t fmoe_expert_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k);

@@ -111,7 +111,7 @@ def test_expert_backward_skips_out_of_range_ids():
     from flash_moe_b200 import read_status, _lib
 
     x, d, u, idx, gates, dout = expert_case(40, 64, 20, 4, torch.float32, seed=3)
-    idx[3, 2] = -1
+    idx[3, 2] = -2
     idx[7, 0] = 20
     read_status()
     got = run_expert_backward(x, d, u, idx, gates, dout)

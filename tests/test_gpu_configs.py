@@ -59,7 +59,7 @@ def zipf_indices(T, k, N, seed, device):
 def test_config4_experts_one_million_zipf():
     """Config 4 on one GPU: 32768 tokens, hidden 2048, N = 2^20 experts (2 x 4 GiB tables), k = 16,
     Zipf(1.1) expert popularity (one expert owns ~12 % of the pairs, most experts are empty), softmax
-    gates.  Takes the expert-centric (sorted) schedule.  Checked exactly on a token sample, by
+    gates.  Tables far larger than L2, gathered per token.  Checked exactly on a token sample, by
     linearity in the gates on all tokens, and for run-to-run determinism."""
     from flash_moe_b200 import check_status
     from flash_moe_b200.ops.flash_expert import flash_expert_fp32

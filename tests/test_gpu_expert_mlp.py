@@ -88,6 +88,18 @@ def test_expert_out_of_range_ids_are_skipped_and_flagged():
     want = O.expert_forward(x, d, u, bad.clamp(0, N - 1), g2)
     assert O.rel_rms_error(got.cpu(), want) < 1e-4
     assert read_status() == 0
+    # -1 alone is the empty-slot value: skipped without raising the flag, in both dtypes' schedules
+    for dtype in (torch.bfloat16, torch.float32):
+        x, d, u, idx, gates = expert_inputs(T, H, N, k, dtype, seed=2)
+        empty = idx.clone()
+        empty[5, 0] = -1
+        empty[7, :] = -1
+        got = flash_expert_fp32(x.cuda(), d.cuda(), u.cuda(), empty.cuda(), gates.cuda())
+        assert read_status() == 0
+        g2 = gates.clone()
+        g2[empty == -1] = 0
+        assert O.rel_rms_error(got.cpu(), O.expert_forward(x, d, u, empty.clamp(0, N - 1), g2)) < 1e-4
+        assert float(got[7].abs().max()) == 0.0
 
 
 def test_expert_matches_reference_kernel_fixture(golden_dir):

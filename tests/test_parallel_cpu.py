@@ -44,8 +44,9 @@ def test_plan_dispatch_sends_each_token_once_per_owner():
             mine = [(int(e) // world, float(w)) for e, w in zip(idx[token], gates[token]) if 0 <= e < N and e % world == dest]
             got = [(int(e), float(w)) for e, w in zip(ids[off + row], gts[off + row]) if w != 0]
             assert sorted(mine) == sorted(got)
-            # padded slots (gate 0) repeat one of the token's own local ids instead of piling up on id 0
-            assert {int(e) for e in ids[off + row]} == {e for e, _ in mine}
+            # the other slots are empty: id -1, gate 0
+            assert {int(e) for e in ids[off + row]} - {-1} == {e for e, _ in mine}
+            assert all(float(w) == 0 for e, w in zip(ids[off + row], gts[off + row]) if int(e) == -1)
             total_pairs += len(mine)
         off += c
     assert total_pairs == int(((idx >= 0) & (idx < N)).sum())
