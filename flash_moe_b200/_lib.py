@@ -80,6 +80,7 @@ SIGNATURES = {
     "fmoe_router_front": (_I, [_P, _P, _P, _P, _I, _F, _F, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_bn_batch_sums_workspace_bytes": (_Z, [_I]),
     "fmoe_bn_batch_sums": (_I, [_P, _I, _L, _I, _P, _P, _Z, _P]),
+    "fmoe_expert_forward_sharded": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_peer_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_pkm_workspace_bytes": (_Z, [_L, _I]),
     "fmoe_pkm_forward": (_I, [_P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),

@@ -1,8 +1,12 @@
-"""Timing of the expert-sharded path (tables sharded by expert id, all-to-all dispatch/combine) on
-N GPUs of one node, at the shape of the 2^20-expert configuration:
+"""Timing of the expert-sharded paths (tables sharded by expert id) on N GPUs of one node, at the shape of the
+2^20-expert configuration:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m flash_moe_b200.bench_expert_sharded [--tokens 32768 --hidden 2048 --experts 1048576 --top-k 16]
+        -m flash_moe_b200.bench_expert_sharded [--mode a2a|peer] [--tokens 32768 --hidden 2048 --experts 1048576 --top-k 16]
+
+--mode a2a: all-to-all dispatch of token rows and combine of partial rows (ExpertShardedExperts).
+--mode peer: shards in symmetric memory, remote rows read in place over NVLink by the gather kernels
+             (PeerShardedExperts): no exchange at all.
 
 Tokens are split evenly over the ranks, expert ids are Zipf(1.1) distributed, gates are a softmax of
 normal logits.  Rank 0 prints one JSON line: tokens/s over all ranks (max over ranks of the CUDA-event
@@ -18,7 +22,7 @@ import os
 import torch
 import torch.distributed as dist
 
-from .parallel import ExpertShardedExperts, token_shard
+from .parallel import ExpertShardedExperts, PeerShardedExperts, token_shard
 
 
 def main():
@@ -27,6 +31,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--experts", type=int, default=1 << 20)
     ap.add_argument("--top-k", type=int, default=16)
+    ap.add_argument("--mode", default="a2a", choices=["a2a", "peer"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -49,7 +54,16 @@ def main():
     cdf = torch.cumsum(p / p.sum(), 0)
     idx = torch.searchsorted(cdf, torch.rand(e - s, k, generator=g, dtype=torch.float64, device=dev)).clamp_(max=N - 1)
     gates = torch.softmax(torch.randn(e - s, k, generator=g, device=dev), -1).to(dt)
-    layer = ExpertShardedExperts(down, up, N)
+    if args.mode == "peer":
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        layer = PeerShardedExperts(N, H, dt, dev)
+        layer.down_shard.copy_(down)
+        layer.up_shard.copy_(up)
+        del down, up
+        layer.publish()
+        layer.last_stats = {"sent_rows": 0, "received_rows": 0}
+    else:
+        layer = ExpertShardedExperts(down, up, N)
     for _ in range(max(args.warmup, 3)):
         layer.forward(x, idx, gates)
     dist.barrier()
@@ -70,11 +84,12 @@ def main():
         sent = [int(t[0]) for t in allstats]
         recv = [int(t[1]) for t in allstats]
         print(json.dumps({
-            "metric": "expert-sharded experts fwd tokens/s", "value": T / (float(ms) * 1e-3), "unit": "tokens/s",
+            "metric": "expert-sharded experts fwd tokens/s", "mode": args.mode, "value": T / (float(ms) * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "ms_per_step": float(ms), "dtype": "bf16", "data": "synthetic",
             "config": {"tokens": T, "hidden": H, "experts": N, "top_k": k, "ids": "Zipf(1.1)", "tables": "id % world"},
             "rows_sent_per_rank": sent, "rows_received_per_rank": recv,
             "dispatch_bytes_per_rank_max": max(sent) * H * 2, "combine_bytes_per_rank_max": max(recv) * H * 4,
+            "peer_row_bytes_per_rank": (2 * (e - s) * k * H * 2 * (world - 1) // world) if args.mode == "peer" else 0,
         }))
     dist.barrier()
     dist.destroy_process_group()

@@ -181,6 +181,16 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
                         static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_expert_forward_sharded(const void* x, const void* const* down_shards, const void* const* up_shards,
+                                int num_shards, const int64_t* indices, const void* gates, void* out, int dtype,
+                                int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k,
+                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_expert_forward_peer(x, down_shards, up_shards, num_shards, indices, gates, out, dtype, out_dtype,
+                                    num_tokens, hidden, num_experts, top_k, workspace, workspace_bytes, status,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int fmoe_peer_forward(const void* x, const void* down, const void* up, const void* routing_weights,
                       const int64_t* indices, void* out, int dtype, int64_t num_tokens, int hidden, int64_t num_experts,
                       int top_k, void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {

@@ -121,6 +121,11 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
                           size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr,
                           int act = 0);
+// the same sum with both tables sharded by e % world over the GPUs of a node; *_shards are DEVICE arrays of `world`
+// row-0 pointers (peer pointers for the other GPUs); 16-bit dtypes only
+int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
+                               const int64_t* indices, const void* gates, void* out, int dtype, int out_dtype, int64_t T,
+                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream);
 // out[t] = sum_j weights[t,j] * values[indices[t,j]] (the PKM comparison op)
 int launch_weighted_rows(const void* values, const void* weights, const int64_t* indices, void* out, int dtype,
                          int64_t T, int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status,

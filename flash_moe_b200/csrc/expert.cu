@@ -247,16 +247,30 @@ template <> struct Mma16816<__half> {
   }
 };
 
+// Row e of a table that is either one array or, PEER, sharded over the GPUs of a node by e % world (shard r holds
+// expert e at row e / world; shards[r] may point into a peer GPU's memory, read with plain loads over NVLink).
+template <typename T, bool PEER>
+__device__ __forceinline__ const T* table_row(const T* table, const T* const* shards, int world, int64_t e, int H) {
+  if constexpr (PEER) {
+    const int64_t local = e / world;
+    return shards[e - local * world] + local * H;
+  } else {
+    return table + e * H;
+  }
+}
+
 // One warp per (token, group of 16 of its experts).  The token's x row is parked in the warp's
 // slice of shared memory (read back as B fragments right before each MMA), so every register that
 // waits for data waits for a gathered down row: batches of UNROLL 32-column blocks keep
 // 2 * UNROLL x 16 B per lane in flight to cover the L2 latency of the gather.
-template <typename T, int UNROLL>
+template <typename T, int UNROLL, bool PEER = false>
 __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restrict__ x, const T* __restrict__ down,
                                                                const int64_t* __restrict__ idx,
                                                                const T* __restrict__ gates, float* __restrict__ gs,
                                                                int64_t ntok, int H, int64_t N, int k, int xs_stride,
-                                                               int32_t* status, int act) {
+                                                               int32_t* status, int act,
+                                                               const T* const* __restrict__ shards = nullptr,
+                                                               int world = 1) {
   extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -278,8 +292,8 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
     const bool oka = (ja < k) && ea >= 0 && ea < N;
     const bool okb = (jb < k) && eb >= 0 && eb < N;
     if ((ja < k && !oka && ea != -1) || (jb < k && !okb && eb != -1)) bad = true;  // -1: empty slot, no flag
-    const T* ra = down + (oka ? ea : 0) * H + 8 * tq;
-    const T* rb = down + (okb ? eb : 0) * H + 8 * tq;
+    const T* ra = table_row<T, PEER>(down, shards, world, oka ? ea : 0, H) + 8 * tq;
+    const T* rb = table_row<T, PEER>(down, shards, world, okb ? eb : 0, H) + 8 * tq;
     if (t != t_in_smem) {  // warp-uniform
       __syncwarp();
       const T* xr = x + t * H;
@@ -333,10 +347,12 @@ __device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t a, uint64_t b) {
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
-template <typename T, typename OutT, int NCH>
+template <typename T, typename OutT, int NCH, bool PEER = false>
 __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
                                                           const float* __restrict__ gs, OutT* __restrict__ out,
-                                                          int64_t ntok, int H, int64_t N, int k, int colblocks) {
+                                                          int64_t ntok, int H, int64_t N, int k, int colblocks,
+                                                          const T* const* __restrict__ shards = nullptr,
+                                                          int world = 1) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int SLOTS = NCH >= 4 ? 4 : 8;
   const int lane = threadIdx.x & 31;
@@ -377,7 +393,7 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
           const int e = __shfl_sync(kFull, e_l, s + u);
           const float w = __shfl_sync(kFull, w_l, s + u);
           ww[u] = pack_f32x2(w, w);
-          const T* row = up + static_cast<int64_t>(e) * H + col0 + lane * VEC;
+          const T* row = table_row<T, PEER>(up, shards, world, e, H) + col0 + lane * VEC;
 #pragma unroll
           for (int c = 0; c < NCH; ++c) q[u][c] = in[c] ? ldg16(row + c * 32 * VEC) : make_uint4(0, 0, 0, 0);
         }
@@ -468,7 +484,7 @@ void launch_accum(const void* up, const int64_t* idx, const float* gs, void* out
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
   expert_accum_kernel<T, OutT, NCH><<<grid, 128, 0, stream>>>(static_cast<const T*>(up), idx, gs,
-                                                              static_cast<OutT*>(out), T_, H, N, k, colblocks);
+                                                              static_cast<OutT*>(out), T_, H, N, k, colblocks, nullptr, 1);
 }
 
 // 16-bit tables are gathered per token (no sort, tensor-core dot products) whatever their size: measured against
@@ -536,7 +552,8 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       auto kern = expert_scores_mma_kernel<T, 8>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
-                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act);
+                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act,
+                                        nullptr, 1);
       FMOE_LAUNCH_CHECK();
     }
     return FMOE_OK;
@@ -807,6 +824,53 @@ __global__ void __launch_bounds__(256) expert_bwd_finish_kernel(const int* __res
   }
 }
 
+// Tables sharded over the GPUs of one node, rows of the other GPUs read through peer pointers: the two gather
+// kernels of the per-token schedule with the row address computed from (e % world, e / world).
+template <typename T>
+int run_typed_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
+                   const int64_t* idx, const void* gates, void* out, int out_f32, int64_t T_, int H, int64_t N, int k,
+                   const ExpertWs& w, int32_t* status, cudaStream_t stream) {
+  if constexpr (sizeof(T) != 2) {
+    return FMOE_ERR_UNSUPPORTED;
+  } else {
+    constexpr int VEC = Vec16<T>::N;
+    const int sms = device_sm_count();
+    {
+      const int64_t want = (T_ * ((k + 15) / 16) + 3) / 4;
+      const int64_t cap = static_cast<int64_t>(sms) * 16;
+      const int grid = static_cast<int>(want < cap ? want : cap);
+      const int xs_stride = ((H + 255) / 256) * 32;
+      const int smem = 4 * xs_stride * 16;
+      auto kern = expert_scores_mma_kernel<T, 8, true>;
+      if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), nullptr, idx, static_cast<const T*>(gates), w.gs, T_, H,
+                                        N, k, xs_stride, status, kActSilu,
+                                        reinterpret_cast<const T* const*>(down_shards), world);
+      FMOE_LAUNCH_CHECK();
+    }
+    const int need = (H + 32 * VEC - 1) / (32 * VEC);
+    const int nch = need <= 1 ? 1 : 2;
+    const int colblocks = (H + 32 * VEC * nch - 1) / (32 * VEC * nch);
+    const int64_t want = (T_ * colblocks + 3) / 4;
+    const int64_t cap = static_cast<int64_t>(sms) * 16;
+    const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+    const T* const* us = reinterpret_cast<const T* const*>(up_shards);
+#define FMOE_PEER_ACCUM(OUT_, NCH_)                                                                                \
+  expert_accum_kernel<T, OUT_, NCH_, true><<<grid, 128, 0, stream>>>(nullptr, idx, w.gs, static_cast<OUT_*>(out), T_, \
+                                                                     H, N, k, colblocks, us, world)
+    if (out_f32) {
+      if (nch == 1) FMOE_PEER_ACCUM(float, 1);
+      else FMOE_PEER_ACCUM(float, 2);
+    } else {
+      if (nch == 1) FMOE_PEER_ACCUM(T, 1);
+      else FMOE_PEER_ACCUM(T, 2);
+    }
+#undef FMOE_PEER_ACCUM
+    FMOE_LAUNCH_CHECK();
+    return FMOE_OK;
+  }
+}
+
 template <typename T>
 __global__ void weights_to_f32_kernel(const T* __restrict__ w, float* __restrict__ out, int64_t n) {
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -1040,6 +1104,33 @@ int launch_weighted_rows(const void* values, const void* weights, const int64_t*
     case FMOE_DTYPE_F16: return run_weighted_rows<__half>(values, weights, indices, out, T, H, N, k, coef, stream);
     default: return FMOE_ERR_BAD_ARG;
   }
+}
+
+int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
+                               const int64_t* indices, const void* gates, void* out, int dtype, int out_dtype, int64_t T,
+                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+  if (T < 0 || H <= 0 || N <= 0 || k < 0 || world < 1) return FMOE_ERR_BAD_ARG;
+  if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
+  if (dtype == FMOE_DTYPE_F32) return FMOE_ERR_UNSUPPORTED;
+  if (T == 0) return FMOE_OK;
+  if (x == nullptr || down_shards == nullptr || up_shards == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
+  if (k > 0 && (indices == nullptr || gates == nullptr)) return FMOE_ERR_BAD_ARG;
+  if (N > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
+  if (H % 8 != 0 || !aligned16(x) || !aligned16(out)) return FMOE_ERR_ALIGNMENT;
+  if (k == 0) {
+    FMOE_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(T) * H * dtype_size(out_dtype), stream));
+    return FMOE_OK;
+  }
+  const ExpertWs w = carve(ws, T, N, k);
+  if (ws == nullptr || ws_bytes < w.bytes) return FMOE_ERR_WORKSPACE;
+  const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
+  if (dtype == FMOE_DTYPE_BF16)
+    return run_typed_peer<__nv_bfloat16>(x, down_shards, up_shards, world, indices, gates, out, out_f32, T, H, N, k, w,
+                                         status, stream);
+  if (dtype == FMOE_DTYPE_F16)
+    return run_typed_peer<__half>(x, down_shards, up_shards, world, indices, gates, out, out_f32, T, H, N, k, w, status,
+                                  stream);
+  return FMOE_ERR_BAD_ARG;
 }
 
 }  // namespace fmoe

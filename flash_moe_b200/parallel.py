@@ -10,7 +10,9 @@ Two ways the path shards (the reference itself has no distributed code):
   each token row is sent ONCE to every rank that owns at least one of its experts together with
   its k (local id, gate) slots, the owner evaluates its local experts, and the partial `[H]`
   rows come back and are summed in float32 (`ExpertShardedExperts`).  Exchanges are
-  `all_to_all_single` calls (NCCL on GPUs, gloo in the CPU tests).
+  `all_to_all_single` calls (NCCL on GPUs, gloo in the CPU tests).  On the GPUs of ONE node the same
+  layout needs no exchange at all: `PeerShardedExperts` keeps the shards in symmetric memory and the
+  gather kernels read the rows of the other GPUs through peer pointers over NVLink.
 """
 
 from __future__ import annotations
@@ -115,4 +117,68 @@ class ExpertShardedExperts:
         self.last_stats = {"sent_rows": sum(counts), "received_rows": rows,
                            "dispatch_bytes": sum(counts) * x.shape[1] * x.element_size(),
                            "combine_bytes": rows * x.shape[1] * 4}
+        return out
+
+
+class PeerShardedExperts:
+    """Fine-grained experts with the tables sharded by `id % world` over the GPUs of one node and read in place:
+    every rank maps the other ranks' shards (torch symmetric memory, no multicast) and the two gather kernels
+    address row `id // world` of shard `id % world` directly, so a token never leaves its GPU and there is no
+    dispatch, no all-to-all and no host-side planning.  The result equals the unsharded op bit for bit.
+
+    Build it collectively (every rank of `group`), fill `down_shard` / `up_shard` (views of this rank's symmetric
+    buffers, `[rows_per_rank, H]`) with `shard_expert_table(table, rank, world)`, then call `publish()` once.
+    """
+
+    def __init__(self, num_experts: int, hidden: int, dtype: torch.dtype, device, group=None):
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("peer-sharded experts support bfloat16 and float16 tables")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+        group = dist.group.WORLD if group is None else group
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_experts, self.hidden, self.dtype = num_experts, hidden, dtype
+        self.device = torch.device(device)
+        self.rows_per_rank = (num_experts + self.world - 1) // self.world
+        self.my_rows = (num_experts - self.rank + self.world - 1) // self.world
+        self._buffers, self._handles, self._ptr_arrays = [], [], []
+        for _ in range(2):
+            buf = symm_mem.empty(self.rows_per_rank, hidden, dtype=dtype, device=self.device)
+            hdl = symm_mem.rendezvous(buf, group)
+            self._buffers.append(buf)
+            self._handles.append(hdl)
+            self._ptr_arrays.append(torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=self.device))
+        self.down_shard = self._buffers[0][: self.my_rows]
+        self.up_shard = self._buffers[1][: self.my_rows]
+
+    def publish(self) -> None:
+        """Make this rank's shard contents visible to the others: finish the copies, then meet at a barrier."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, gates: torch.Tensor, out_dtype=None) -> torch.Tensor:
+        """x [T_local, H], indices [T_local, k] (global ids), gates [T_local, k] -> [T_local, H] (x.dtype or float32)."""
+        from . import _lib
+
+        dev = _lib.require_cuda(x, indices, gates)
+        x, idx, g = x.contiguous(), indices.contiguous().to(torch.int64), gates.contiguous().to(x.dtype)
+        if x.dtype != self.dtype or x.shape[1] != self.hidden:
+            raise _lib.FmoeError("x must match the tables' dtype and hidden size")
+        T, k = idx.shape
+        out_dtype = x.dtype if out_dtype is None else out_dtype
+        out = torch.empty((T, self.hidden), device=dev, dtype=out_dtype)
+        L = _lib.lib()
+        ws_bytes = L.fmoe_expert_workspace_bytes(T, self.hidden, self.num_experts, k)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            rc = L.fmoe_expert_forward_sharded(
+                x.data_ptr(), self._ptr_arrays[0].data_ptr(), self._ptr_arrays[1].data_ptr(), self.world, idx.data_ptr(),
+                g.data_ptr(), out.data_ptr(), _lib.dtype_code(x), _lib.DTYPE_CODE[out_dtype], T, self.hidden,
+                self.num_experts, k, ws.data_ptr(), ws_bytes, _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev))
+        _lib.check(rc, "fmoe_expert_forward_sharded")
         return out

@@ -158,6 +158,19 @@ int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t
                               int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * fmoe_expert_forward with both tables sharded over the GPUs of one node by expert id: shard r = id % num_shards
+ * holds expert id at row id / num_shards.  down_shards / up_shards are DEVICE arrays of num_shards pointers to row
+ * 0 of each shard; the entries of the other GPUs are peer-mapped pointers (CUDA IPC / symmetric memory), which the
+ * gather kernels read with plain loads over NVLink - no dispatch, no all-to-all, no host planning.  Every GPU calls
+ * it for its own tokens.  bf16 / fp16 only; workspace as for fmoe_expert_forward.  The reference has no multi-GPU
+ * code; the result equals fmoe_expert_forward on the unsharded tables bit for bit.
+ */
+int fmoe_expert_forward_sharded(const void* x, const void* const* down_shards, const void* const* up_shards,
+                                int num_shards, const int64_t* indices, const void* gates, void* out, int dtype,
+                                int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k,
+                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+
+/*
  * fmoe_expert_forward without a caller-supplied workspace.  It has no counterpart in the
  * reference; it exists for hosts that cannot allocate device memory where they call the library
  * (a frozen memory plan after warm-up, a fixed real-time budget, a language binding without a

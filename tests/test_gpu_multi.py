@@ -78,3 +78,54 @@ def test_two_gpu_token_and_expert_sharding(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("ok") == 2
+
+
+PEER_WORKER = textwrap.dedent(
+    """
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["FMOE_ROOT"])
+    from flash_moe_b200 import check_status
+    from flash_moe_b200.parallel import PeerShardedExperts, shard_expert_table, token_shard
+    from flash_moe_b200.ops.flash_expert import flash_expert_fp32, flash_expert_func
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(3)
+    T, H, N, k = 512, 256, 4099, 8            # an expert count the world size does not divide
+    xs = (torch.randn(T, H, generator=g) * 0.5).to(dt).to(dev)
+    down = (torch.randn(N, H, generator=g) * 0.1).to(dt).to(dev)
+    up = (torch.randn(N, H, generator=g) * 0.1).to(dt).to(dev)
+    idx = torch.randint(0, N, (T, k), generator=g).to(dev)
+    idx[0, 0] = N - 1
+    idx[1, 1] = -1                            # an empty slot
+    gates = torch.softmax(torch.randn(T, k, generator=g), -1).to(dt).to(dev)
+    want32 = flash_expert_fp32(xs, down, up, idx, gates)
+    want16 = flash_expert_func(xs, down, up, idx, gates)
+    layer = PeerShardedExperts(N, H, dt, dev)
+    layer.down_shard.copy_(shard_expert_table(down, rank, world))
+    layer.up_shard.copy_(shard_expert_table(up, rank, world))
+    layer.publish()
+    s, e = token_shard(T, rank, world)
+    got32 = layer.forward(xs[s:e], idx[s:e], gates[s:e], out_dtype=torch.float32)
+    got16 = layer.forward(xs[s:e], idx[s:e], gates[s:e])
+    torch.cuda.synchronize(); check_status()
+    assert torch.equal(got32, want32[s:e]) and torch.equal(got16, want16[s:e]), "peer-sharded result differs"
+    dist.barrier(); dist.destroy_process_group()
+    print("rank", rank, "peer ok")
+    """
+)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_peer_memory_expert_sharding(tmp_path):
+    """Tables sharded over two GPUs and read in place through peer pointers: bit-equal to the unsharded op."""
+    script = tmp_path / "peer_worker.py"
+    script.write_text(PEER_WORKER)
+    env = dict(os.environ, FMOE_ROOT=ROOT, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29743", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("peer ok") == 2
