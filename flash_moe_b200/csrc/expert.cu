@@ -697,11 +697,11 @@ __global__ void __launch_bounds__(128) expert_bwd_tables_kernel(
     bool in[NCH];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) in[c] = col0 + (c * 32 + lane) * VEC < H;
-    float ad[NCH][VEC], au[NCH][VEC];
+    uint64_t ad[NCH][VEC / 2], au[NCH][VEC / 2];  // packed pairs of float32 sums (fma.rn.f32x2)
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) ad[c][i] = au[c][i] = 0.f;
+      for (int i = 0; i < VEC / 2; ++i) ad[c][i] = au[c][i] = 0ull;
 
     int cur_e = sorted_expert[pos0];
     bool began_earlier = offsets[cur_e] < pos0;
@@ -711,20 +711,25 @@ __global__ void __launch_bounds__(128) expert_bwd_tables_kernel(
       for (int c = 0; c < NCH; ++c) {
         const int col = col0 + (c * 32 + lane) * VEC;
         if (!in[c]) continue;
+        float fd[VEC], fu[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) {
+          unpack_f32x2(ad[c][i], fd[2 * i], fd[2 * i + 1]);
+          unpack_f32x2(au[c][i], fu[2 * i], fu[2 * i + 1]);
+          ad[c][i] = au[c][i] = 0ull;
+        }
         if (partial) {
           float* pd = partial_d + (chunk * 2 + slot) * H + col;
           float* pu = partial_u + (chunk * 2 + slot) * H + col;
 #pragma unroll
           for (int i = 0; i < VEC; i += 4) {
-            *reinterpret_cast<float4*>(pd + i) = make_float4(ad[c][i], ad[c][i + 1], ad[c][i + 2], ad[c][i + 3]);
-            *reinterpret_cast<float4*>(pu + i) = make_float4(au[c][i], au[c][i + 1], au[c][i + 2], au[c][i + 3]);
+            *reinterpret_cast<float4*>(pd + i) = make_float4(fd[i], fd[i + 1], fd[i + 2], fd[i + 3]);
+            *reinterpret_cast<float4*>(pu + i) = make_float4(fu[i], fu[i + 1], fu[i + 2], fu[i + 3]);
           }
         } else {
-          *reinterpret_cast<uint4*>(ddown + static_cast<int64_t>(e) * H + col) = pack16<T>(ad[c]);
-          *reinterpret_cast<uint4*>(dup + static_cast<int64_t>(e) * H + col) = pack16<T>(au[c]);
+          *reinterpret_cast<uint4*>(ddown + static_cast<int64_t>(e) * H + col) = pack16<T>(fd);
+          *reinterpret_cast<uint4*>(dup + static_cast<int64_t>(e) * H + col) = pack16<T>(fu);
         }
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) ad[c][i] = au[c][i] = 0.f;
       }
     };
 
@@ -764,15 +769,16 @@ __global__ void __launch_bounds__(128) expert_bwd_tables_kernel(
         began_earlier = false;
       }
       const float wd = ds[p], wu = gs[p];
+      const uint64_t wd2 = pack_f32x2(wd, wd), wu2 = pack_f32x2(wu, wu);
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         float xf[VEC], of[VEC];
         unpack16<T>(xq[c], xf);
         unpack16<T>(oq[c], of);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          ad[c][i] = fmaf(wd, xf[i], ad[c][i]);
-          au[c][i] = fmaf(wu, of[i], au[c][i]);
+        for (int i = 0; i < VEC / 2; ++i) {
+          ffma2(ad[c][i], pack_f32x2(xf[2 * i], xf[2 * i + 1]), wd2);
+          ffma2(au[c][i], pack_f32x2(of[2 * i], of[2 * i + 1]), wu2);
         }
       }
     }
