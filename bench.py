@@ -37,7 +37,7 @@ L2_FLUSH_BYTES = 256 << 20
 NCU_DRAM_BYTES = {
     "router_front": 8404992 + 8931072,  # bn_apply + router GEMM
     "router_topk": 2168576,
-    "expert_scores": 44577024 + 57088,
+    "expert_scores": 44580096 + 82944,
     "expert_accum": 36716544 + 321024,
     "mlp_up": 25196032 + 64256,
     "mlp_down": 58740224 + 1576960,
@@ -45,7 +45,7 @@ NCU_DRAM_BYTES = {
 KERNEL_OF_STAGE = {
     "router_front": "bn_apply_kernel + gemm_tcgen05_kernel<128, ROUTER> (batch-norm, sub-key logits)",
     "router_topk": "router_topk_reg_kernel<bf16, 4> (log-softmax, product-key top-k, gates)",
-    "expert_scores": "expert_scores_mma_kernel<bf16, 8> (gathered down rows x token row, silu * gate)",
+    "expert_scores": "expert_scores_mma_kernel<bf16, 4 x 2 buffers> (gathered down rows x token row, silu * gate)",
     "expert_accum": "expert_accum_kernel<bf16, float, 2> (gate-weighted sum of gathered up rows)",
     "mlp_up": "gemm_tcgen05_pair_kernel<SWIGLU> (shared MLP gate/up GEMM + SiLU*up epilogue, CTA pairs)",
     "mlp_down": "gemm_tcgen05_pair_kernel<ADD> (shared MLP down GEMM + fp32 expert addend, CTA pairs)",

@@ -261,9 +261,10 @@ __device__ __forceinline__ const T* table_row(const T* table, const T* const* sh
 
 // One warp per (token, group of 16 of its experts).  The token's x row is parked in the warp's
 // slice of shared memory (read back as B fragments right before each MMA), so every register that
-// waits for data waits for a gathered down row: batches of UNROLL 32-column blocks keep
-// 2 * UNROLL x 16 B per lane in flight to cover the L2 latency of the gather.
-template <typename T, int UNROLL, bool PEER = false>
+// waits for data waits for a gathered down row: batches of UNROLL 32-column blocks (2 * UNROLL x 16 B per lane) in
+// STAGES register buffers keep gathers in flight across batches to cover the L2 latency (measured at the
+// benchmark shape: 4 x 2 buffers 57.7 us, 8 x 1 61.9 us, 4 x 3 62.6 us, 2 x 2 57.8 us).
+template <typename T, int UNROLL, bool PEER = false, int STAGES = 1>
 __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restrict__ x, const T* __restrict__ down,
                                                                const int64_t* __restrict__ idx,
                                                                const T* __restrict__ gates, float* __restrict__ gs,
@@ -302,8 +303,7 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
       t_in_smem = t;
     }
     float c[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c0 = 0; c0 < H; c0 += 32 * UNROLL) {
-      uint4 qa[UNROLL], qb[UNROLL];
+    auto load = [&](uint4 (&qa)[UNROLL], uint4 (&qb)[UNROLL], int c0) {
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int col = c0 + 32 * u;
@@ -311,12 +311,33 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
         qa[u] = in ? ldg16(ra + col) : make_uint4(0, 0, 0, 0);
         qb[u] = in ? ldg16(rb + col) : make_uint4(0, 0, 0, 0);
       }
+    };
+    auto consume = [&](const uint4 (&qa)[UNROLL], const uint4 (&qb)[UNROLL], int c0) {
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int piece = ((c0 + 32 * u) >> 3) + tq;
         const uint4 xq = piece < xs_stride ? xs[piece] : make_uint4(0, 0, 0, 0);
         Mma16816<T>::run(c, qa[u].x, qb[u].x, qa[u].y, qb[u].y, xq.x, xq.y);
         Mma16816<T>::run(c, qa[u].z, qb[u].z, qa[u].w, qb[u].w, xq.z, xq.w);
+      }
+    };
+    if constexpr (STAGES == 2) {
+      // two register buffers: the next batch of gathers is issued before the current one is consumed, so the
+      // loads in flight never drain between batches (same column order, hence the same sums)
+      constexpr int STEP = 32 * UNROLL;
+      uint4 a0[UNROLL], b0[UNROLL], a1[UNROLL], b1[UNROLL];
+      load(a0, b0, 0);
+      for (int c0 = 0; c0 < H; c0 += 2 * STEP) {
+        if (c0 + STEP < H) load(a1, b1, c0 + STEP);
+        consume(a0, b0, c0);
+        if (c0 + 2 * STEP < H) load(a0, b0, c0 + 2 * STEP);
+        if (c0 + STEP < H) consume(a1, b1, c0 + STEP);
+      }
+    } else {
+      for (int c0 = 0; c0 < H; c0 += 32 * UNROLL) {
+        uint4 qa[UNROLL], qb[UNROLL];
+        load(qa, qb, c0);
+        consume(qa, qb, c0);
       }
     }
     if (tq == 0) {
@@ -385,9 +406,7 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
         }
       }
       const int nslots = min(32, k - j0);
-      for (int s = 0; s < nslots; s += SLOTS) {
-        uint4 q[SLOTS][NCH];
-        uint64_t ww[SLOTS];
+      auto load = [&](uint4 (&q)[SLOTS][NCH], uint64_t (&ww)[SLOTS], int s) {
 #pragma unroll
         for (int u = 0; u < SLOTS; ++u) {
           const int e = __shfl_sync(kFull, e_l, s + u);
@@ -397,6 +416,8 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
 #pragma unroll
           for (int c = 0; c < NCH; ++c) q[u][c] = in[c] ? ldg16(row + c * 32 * VEC) : make_uint4(0, 0, 0, 0);
         }
+      };
+      auto consume = [&](const uint4 (&q)[SLOTS][NCH], const uint64_t (&ww)[SLOTS]) {
 #pragma unroll
         for (int u = 0; u < SLOTS; ++u)
 #pragma unroll
@@ -406,6 +427,13 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
 #pragma unroll
             for (int i = 0; i < VEC / 2; ++i) ffma2(acc[c][i], pack_f32x2(f[2 * i], f[2 * i + 1]), ww[u]);
           }
+      };
+      // one batch of SLOTS gathered rows at a time (a second register buffer was measured slower: 64 vs 52 us)
+      for (int s = 0; s < nslots; s += SLOTS) {
+        uint4 q[SLOTS][NCH];
+        uint64_t ww[SLOTS];
+        load(q, ww, s);
+        consume(q, ww);
       }
     }
     OutT* orow = out + t * H + col0;
@@ -549,7 +577,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       const int grid = static_cast<int>(want < cap ? want : cap);
       const int xs_stride = ((H + 255) / 256) * 32;  // uint4 per warp, rows padded to 256 columns
       const int smem = 4 * xs_stride * 16;
-      auto kern = expert_scores_mma_kernel<T, 8>;
+      auto kern = expert_scores_mma_kernel<T, 4, false, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
                                         static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act,
@@ -847,7 +875,7 @@ int run_typed_peer(const void* x, const void* const* down_shards, const void* co
       const int grid = static_cast<int>(want < cap ? want : cap);
       const int xs_stride = ((H + 255) / 256) * 32;
       const int smem = 4 * xs_stride * 16;
-      auto kern = expert_scores_mma_kernel<T, 8, true>;
+      auto kern = expert_scores_mma_kernel<T, 4, true, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), nullptr, idx, static_cast<const T*>(gates), w.gs, T_, H,
                                         N, k, xs_stride, status, kActSilu,
