@@ -37,7 +37,7 @@ L2_FLUSH_BYTES = 256 << 20
 NCU_DRAM_BYTES = {
     "router_front": 8404992 + 8931072,  # bn_apply + router GEMM
     "router_topk": 2168576,
-    "expert_scores": 44580096 + 82944,
+    "expert_scores": 44579328 + 82944,
     "expert_accum": 36716544 + 321024,
     "mlp_up": 25196032 + 64256,
     "mlp_down": 58740224 + 1576960,
