@@ -238,6 +238,11 @@ int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da,
   return launch_swiglu_backward(dh, a, b, da, db, h, dtype, num_elements, static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
+                      float* sink, fmoe_stream_t stream) {
+  return launch_gather_probe(table, row_ids, count, row_bytes, ctas_per_sm, sink, static_cast<cudaStream_t>(stream));
+}
+
 int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,
                               int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream) {
   return launch_combine_rows(rows, num_rows, slot, num_sources, num_tokens, hidden, out, status,

@@ -163,6 +163,8 @@ int launch_router_topk_backward(const void* dscores, const int64_t* indices, int
                                 void* dlog_probs, cudaStream_t stream);
 int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
                            int64_t n, cudaStream_t stream);
+int launch_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
+                        float* sink, cudaStream_t stream);
 int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
                         float* out, int32_t* status, cudaStream_t stream);
 

@@ -147,6 +147,16 @@ int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da,
                          int64_t num_elements, fmoe_stream_t stream);
 
 /*
+ * Measurement aid, no counterpart in the reference: a load-only kernel with the access pattern of the two expert
+ * passes (random rows of `row_bytes` = 512, 1024, 2048 or 4096 bytes of `table`, ids in row_ids[count], fetched with
+ * 16-byte loads by device_sms * ctas_per_sm CTAs of 128 threads).  count * row_bytes / its duration is the rate at which
+ * this GPU can bring gathered rows to its SMs - the ceiling the expert kernels are measured against when the tables are
+ * resident in L2.  `sink` (nullable) is one float that is never written in practice.
+ */
+int fmoe_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
+                      float* sink, fmoe_stream_t stream);
+
+/*
  * Combine step of the expert-sharded layout (tables split over GPUs by expert id, token rows sent to
  * the owners, partial results sent back): out[t] = sum_g rows[slot[g * num_tokens + t]], skipping
  * slot < 0, sources added in ascending g in float32.  rows [num_rows, hidden] float32 are the partial

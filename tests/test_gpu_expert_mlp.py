@@ -166,3 +166,15 @@ def test_combine_partial_rows_sums_in_source_order(T, H, G):
     assert torch.equal(got.cpu(), want)
     with pytest.raises(Exception):
         combine_partial_rows(rows.cuda().to(torch.bfloat16), slot.cuda(), T)
+
+
+def test_gather_roof_probe_runs_and_rejects_bad_rows():
+    from flash_moe_b200 import _lib
+    from flash_moe_b200.bench_gather_roof import measure_gather_roof
+
+    best, per_grid = measure_gather_roof("cuda:0", row_bytes=1024, rows=4096, count=65536, reps=2)
+    assert best > 100.0 and len(per_grid) == 4  # GB/s; any working GPU is far above this
+    t = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    ids = torch.zeros(8, dtype=torch.int32, device="cuda")
+    rc = _lib.lib().fmoe_gather_probe(t.data_ptr(), ids.data_ptr(), 8, 768, 4, None, _lib.current_stream_ptr(t.device))
+    assert rc == 4  # FMOE_ERR_ALIGNMENT: rows must be multiples of 512 bytes
