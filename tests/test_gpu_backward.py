@@ -224,3 +224,18 @@ def test_training_step_replays_from_a_cuda_graph():
     assert torch.equal(x.grad, want_x)
     for n, p in layer.named_parameters():
         assert torch.equal(p.grad, want[n]), n
+
+
+def test_backward_with_no_pairs():
+    """k = 0: the expert op's gradients are all zero (and every table row is written)."""
+    from flash_moe_b200.ops.flash_expert import _expert_backward
+
+    dt = torch.float32
+    x, dout = randn((6, 32), 1, dt).cuda(), randn((6, 32), 2, dt).cuda()
+    d, u = randn((10, 32), 3, dt).cuda(), randn((10, 32), 4, dt).cuda()
+    idx = torch.empty(6, 0, dtype=torch.int64, device="cuda")
+    gates = torch.empty(6, 0, dtype=dt, device="cuda")
+    dx, dd, du, dg = _expert_backward(dout, x, d, u, idx, gates)
+    torch.cuda.synchronize()
+    assert float(dx.abs().max()) == 0.0 and float(dd.abs().max()) == 0.0 and float(du.abs().max()) == 0.0
+    assert dg.shape == (6, 0)

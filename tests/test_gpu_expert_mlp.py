@@ -178,3 +178,29 @@ def test_gather_roof_probe_runs_and_rejects_bad_rows():
     ids = torch.zeros(8, dtype=torch.int32, device="cuda")
     rc = _lib.lib().fmoe_gather_probe(t.data_ptr(), ids.data_ptr(), 8, 768, 4, None, _lib.current_stream_ptr(t.device))
     assert rc == 4  # FMOE_ERR_ALIGNMENT: rows must be multiples of 512 bytes
+
+
+def test_empty_inputs():
+    """No tokens, or no experts per token: empty / zero results, no launch errors."""
+    from flash_moe_b200 import FlashMoE, FlashMoEConfig, check_status
+    from flash_moe_b200.ops.flash_expert import flash_expert_func
+    from flash_moe_b200.ops.flash_mlp import flash_mlp_func
+    from flash_moe_b200.ops.pkm import pkm_func
+
+    dt = torch.bfloat16
+    d, u = randn((32, 64), 1, dt).cuda(), randn((32, 64), 2, dt).cuda()
+    x0 = torch.empty(0, 64, dtype=dt, device="cuda")
+    idx0 = torch.empty(0, 4, dtype=torch.int64, device="cuda")
+    assert flash_expert_func(x0, d, u, idx0, torch.empty(0, 4, dtype=dt, device="cuda")).shape == (0, 64)
+    x = randn((5, 64), 3, dt).cuda()
+    none = flash_expert_func(x, d, u, torch.empty(5, 0, dtype=torch.int64, device="cuda"), torch.empty(5, 0, dtype=dt, device="cuda"))
+    assert none.shape == (5, 64) and float(none.abs().max()) == 0.0
+    assert float(pkm_func(u, torch.empty(5, 0, dtype=dt, device="cuda"), torch.empty(5, 0, dtype=torch.int64, device="cuda")).abs().max()) == 0.0
+    wg, wu, wd = randn((128, 64), 4, dt).cuda(), randn((128, 64), 5, dt).cuda(), randn((64, 128), 6, dt).cuda()
+    assert flash_mlp_func(x0, wg, wu, wd).shape == (0, 64)
+    layer = FlashMoE(FlashMoEConfig(64, 128, "silu", 64, 4)).to(dt).cuda().eval()
+    with torch.no_grad():
+        y, logits = layer(torch.empty(1, 0, 64, dtype=dt, device="cuda"))
+    assert y.shape == (1, 0, 64) and logits.shape == (2, 0, 8)
+    torch.cuda.synchronize()
+    check_status()

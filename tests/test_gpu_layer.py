@@ -119,7 +119,7 @@ def test_layer_config2_full_size_bf16():
     assert torch.equal(y, y2)
 
 
-def test_state_dict_and_forward_only_contract():
+def test_state_dict_and_device_contract():
     from flash_moe_b200 import FlashMoE, FlashMoEConfig
 
     ref, ours = make_layer_pair(128, 256, 256, 4, False, torch.bfloat16)
