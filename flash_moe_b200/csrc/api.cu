@@ -219,17 +219,28 @@ int fmoe_router_topk_backward(const void* dscores, const int64_t* indices, int d
                                      static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_expert_forward_saving_scores(const void* x, const void* down, const void* up, const int64_t* indices,
+                                      const void* gates, void* out, float* scores_out, int dtype, int out_dtype,
+                                      int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                                      size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_expert_forward(x, down, up, indices, gates, out, dtype, out_dtype, num_tokens, hidden, num_experts,
+                               top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream), nullptr,
+                               kActSilu, scores_out);
+}
+
 size_t fmoe_expert_backward_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k) {
   return expert_backward_workspace_bytes(num_tokens, hidden, num_experts, top_k);
 }
 
 int fmoe_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
-                         const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype,
-                         int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                         const void* gates, const float* saved_scores, void* dx, void* ddown, void* dup, void* dgates,
+                         int dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
                          size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
   if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
   return launch_expert_backward(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, dtype, num_tokens, hidden,
-                                num_experts, top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+                                num_experts, top_k, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream),
+                                saved_scores);
 }
 
 int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,

@@ -120,7 +120,8 @@ size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k);
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
                           size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr,
-                          int act = 0);
+                          int act = 0, float* raw_scores = nullptr);
+// raw_scores (nullable) [T, k] float32 receives <x[t], down[e]> before the activation, for the backward pass.
 // the same sum with both tables sharded by e % world over the GPUs of a node; *_shards are DEVICE arrays of `world`
 // row-0 pointers (peer pointers for the other GPUs); 16-bit dtypes only
 int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
@@ -158,7 +159,8 @@ int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, in
 size_t expert_backward_workspace_bytes(int64_t T, int H, int64_t N, int k);
 int launch_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
                            const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype, int64_t T,
-                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream);
+                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                           const float* saved_scores = nullptr);
 int launch_router_topk_backward(const void* dscores, const int64_t* indices, int dtype, int64_t T, int nk, int k,
                                 void* dlog_probs, cudaStream_t stream);
 int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,

@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
                                                            const int* __restrict__ sorted_expert,
                                                            const int* __restrict__ total_ptr,
                                                            const T* __restrict__ gates, float* __restrict__ gs, int H,
-                                                           int k, int chunk, int act) {
+                                                           int k, int chunk, int act, float* __restrict__ raw_out) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int R = NCH > 0 ? NCH : 1;
   const int lane = threadIdx.x & 31;
@@ -216,7 +216,10 @@ __global__ void __launch_bounds__(256) expert_scores_kernel(const T* __restrict_
       }
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFull, acc, d);
-      if (lane == 0) gs[p] = gates != nullptr ? expert_act(acc, act) * to_f32<T>(gates[p]) : acc;  // nullptr: raw dot product
+      if (lane == 0) {
+        gs[p] = gates != nullptr ? expert_act(acc, act) * to_f32<T>(gates[p]) : acc;  // nullptr: raw dot product
+        if (raw_out != nullptr) raw_out[p] = acc;  // kept for the backward pass
+      }
     }
   }
 }
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
                                                                int64_t ntok, int H, int64_t N, int k, int xs_stride,
                                                                int32_t* status, int act,
                                                                const T* const* __restrict__ shards = nullptr,
-                                                               int world = 1) {
+                                                               int world = 1, float* __restrict__ raw_out = nullptr) {
   extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -344,6 +347,10 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
       if (gates != nullptr) {
         if (ja < k) gs[t * k + ja] = oka ? expert_act(c[0], act) * to_f32<T>(gates[t * k + ja]) : 0.f;
         if (jb < k) gs[t * k + jb] = okb ? expert_act(c[2], act) * to_f32<T>(gates[t * k + jb]) : 0.f;
+        if (raw_out != nullptr) {  // pre-activation scores kept for the backward pass
+          if (ja < k) raw_out[t * k + ja] = oka ? c[0] : 0.f;
+          if (jb < k) raw_out[t * k + jb] = okb ? c[2] : 0.f;
+        }
       } else {  // raw dot products (backward pass)
         if (ja < k) gs[t * k + ja] = oka ? c[0] : 0.f;
         if (jb < k) gs[t * k + jb] = okb ? c[2] : 0.f;
@@ -491,7 +498,7 @@ ExpertWs carve(void* ws, int64_t T, int64_t N, int k) {
 
 template <typename T, int NCH>
 void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N, const void* gates, float* gs_out,
-                   int H, int k, int64_t P, cudaStream_t stream, int act) {
+                   int H, int k, int64_t P, cudaStream_t stream, int act, float* raw_out) {
   const int chunk = 16;
   const int64_t tasks = (P + chunk - 1) / chunk;
   const int64_t want = (tasks + 7) / 8;
@@ -499,7 +506,7 @@ void launch_scores(const void* x, const void* down, const ExpertWs& w, int64_t N
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
   expert_scores_kernel<T, NCH><<<grid, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(down),
                                                          w.sorted_pair, w.sorted_expert, w.offsets + N,
-                                                         static_cast<const T*>(gates), gs_out, H, k, chunk, act);
+                                                         static_cast<const T*>(gates), gs_out, H, k, chunk, act, raw_out);
 }
 
 template <typename T, typename OutT, int NCH>
@@ -565,7 +572,8 @@ int run_sort(const int64_t* idx, int64_t P, int64_t N, const ExpertWs& w, int32_
 // raw dot product.  `sorted` says whether run_sort has filled w for these indices.
 template <typename T>
 int run_scores(const void* rows, const void* table, const int64_t* idx, const void* gates, float* out, int64_t T_, int H,
-               int64_t N, int k, const ExpertWs& w, bool sorted, int32_t* status, cudaStream_t stream, int act = 0) {
+               int64_t N, int k, const ExpertWs& w, bool sorted, int32_t* status, cudaStream_t stream, int act = 0,
+               float* raw_out = nullptr) {
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
@@ -581,7 +589,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
                                         static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act,
-                                        nullptr, 1);
+                                        nullptr, 1, raw_out);
       FMOE_LAUNCH_CHECK();
     }
     return FMOE_OK;
@@ -590,11 +598,11 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
     const int rc = run_sort(idx, P, N, w, status, stream);
     if (rc != FMOE_OK) return rc;
   }
-  if (need <= 1) launch_scores<T, 1>(rows, table, w, N, gates, out, H, k, P, stream, act);
-  else if (need <= 2) launch_scores<T, 2>(rows, table, w, N, gates, out, H, k, P, stream, act);
-  else if (need <= 4) launch_scores<T, 4>(rows, table, w, N, gates, out, H, k, P, stream, act);
-  else if (need <= 8) launch_scores<T, 8>(rows, table, w, N, gates, out, H, k, P, stream, act);
-  else launch_scores<T, 0>(rows, table, w, N, gates, out, H, k, P, stream, act);
+  if (need <= 1) launch_scores<T, 1>(rows, table, w, N, gates, out, H, k, P, stream, act, raw_out);
+  else if (need <= 2) launch_scores<T, 2>(rows, table, w, N, gates, out, H, k, P, stream, act, raw_out);
+  else if (need <= 4) launch_scores<T, 4>(rows, table, w, N, gates, out, H, k, P, stream, act, raw_out);
+  else if (need <= 8) launch_scores<T, 8>(rows, table, w, N, gates, out, H, k, P, stream, act, raw_out);
+  else launch_scores<T, 0>(rows, table, w, N, gates, out, H, k, P, stream, act, raw_out);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }
@@ -621,8 +629,8 @@ int run_accum(const void* table, const int64_t* idx, const float* coef, void* ou
 template <typename T>
 int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
               int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
-              cudaStream_t stream, void* const* between_passes, int act) {
-  int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream, act);
+              cudaStream_t stream, void* const* between_passes, int act, float* raw_scores) {
+  int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream, act, raw_scores);
   if (rc != FMOE_OK) return rc;
   if (between_passes != nullptr)
     for (int i = 0; i < 2; ++i)
@@ -678,10 +686,11 @@ size_t stable_sort_temp_bytes(int64_t P, int64_t N) {
   return bytes;
 }
 
-// in: s (raw <x, D>), q (raw <dout, U>), gates.  out: ds (over s), gs = silu(s) * g (over q), dgates.
+// in: s_in (raw <x, D>; may alias s_ds), q (raw <dout, U>), gates.  out: s_ds = ds, gs = silu(s) * g (over q), dgates.
 template <typename T>
-__global__ void expert_bwd_pairs_kernel(float* __restrict__ s_ds, float* __restrict__ q_gs, const T* __restrict__ gates,
-                                        const int64_t* __restrict__ idx, int64_t N, T* __restrict__ dgates, int64_t P) {
+__global__ void expert_bwd_pairs_kernel(const float* s_in, float* s_ds, float* __restrict__ q_gs,
+                                        const T* __restrict__ gates, const int64_t* __restrict__ idx, int64_t N,
+                                        T* __restrict__ dgates, int64_t P) {
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < P;
        p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t e = idx[p];
@@ -691,7 +700,7 @@ __global__ void expert_bwd_pairs_kernel(float* __restrict__ s_ds, float* __restr
       dgates[p] = from_f32<T>(0.f);
       continue;
     }
-    const float s = s_ds[p], q = q_gs[p], g = to_f32<T>(gates[p]);
+    const float s = s_in[p], q = q_gs[p], g = to_f32<T>(gates[p]);
     const float sig = __fdividef(1.0f, 1.0f + __expf(-s));
     const float act = s * sig;
     s_ds[p] = q * g * (sig * (1.0f + s * (1.0f - sig)));
@@ -879,7 +888,7 @@ int run_typed_peer(const void* x, const void* const* down_shards, const void* co
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), nullptr, idx, static_cast<const T*>(gates), w.gs, T_, H,
                                         N, k, xs_stride, status, kActSilu,
-                                        reinterpret_cast<const T* const*>(down_shards), world);
+                                        reinterpret_cast<const T* const*>(down_shards), world, nullptr);
       FMOE_LAUNCH_CHECK();
     }
     const int need = (H + 32 * VEC - 1) / (32 * VEC);
@@ -975,7 +984,7 @@ void launch_bwd_tables(const void* x, const void* dout, const ExpertBwdWs& w, in
 template <typename T>
 int run_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* idx,
                  const void* gates, void* dx, void* ddown, void* dup, void* dgates, int64_t T_, int H, int64_t N, int k,
-                 const ExpertBwdWs& w, int32_t* status, cudaStream_t stream) {
+                 const ExpertBwdWs& w, int32_t* status, cudaStream_t stream, const float* saved_scores) {
   constexpr int VEC = Vec16<T>::N;
   const int64_t P = T_ * k;
   const int sms = device_sm_count();
@@ -1005,15 +1014,17 @@ int run_backward(const void* dout, const void* x, const void* down, const void* 
                                                   reinterpret_cast<unsigned*>(w.fwd.sorted_expert), w.vals_in,
                                                   w.fwd.sorted_pair, static_cast<int>(P), 0, key_bits(N), stream));
   }
-  rc = run_scores<T>(x, down, idx, nullptr, w.fwd.gs, T_, H, N, k, w.fwd, true, status, stream);
-  if (rc != FMOE_OK) return rc;
+  if (saved_scores == nullptr) {  // s = <x, D[e]> was not kept by the forward: recompute it
+    rc = run_scores<T>(x, down, idx, nullptr, w.fwd.gs, T_, H, N, k, w.fwd, true, status, stream);
+    if (rc != FMOE_OK) return rc;
+  }
   rc = run_scores<T>(dout, up, idx, nullptr, w.q, T_, H, N, k, w.fwd, true, status, stream);
   if (rc != FMOE_OK) return rc;
   {
     const int64_t want = (P + 255) / 256;
     const int grid = static_cast<int>(want < sms * 8 ? want : sms * 8);
-    expert_bwd_pairs_kernel<T><<<grid, 256, 0, stream>>>(w.fwd.gs, w.q, static_cast<const T*>(gates), idx, N,
-                                                        static_cast<T*>(dgates), P);
+    expert_bwd_pairs_kernel<T><<<grid, 256, 0, stream>>>(saved_scores != nullptr ? saved_scores : w.fwd.gs, w.fwd.gs, w.q,
+                                                        static_cast<const T*>(gates), idx, N, static_cast<T*>(dgates), P);
     FMOE_LAUNCH_CHECK();
   }
   rc = run_accum<T>(down, idx, w.fwd.gs, dx, sizeof(T) == 4 ? 1 : 0, T_, H, N, k, stream);
@@ -1043,7 +1054,8 @@ size_t expert_workspace_bytes(int64_t T, int H, int64_t N, int k) {
 
 int launch_expert_forward(const void* x, const void* down, const void* up, const int64_t* indices, const void* gates,
                           void* out, int dtype, int out_dtype, int64_t T, int H, int64_t N, int k, void* ws,
-                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes, int act) {
+                          size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes, int act,
+                          float* raw_scores) {
   if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
   if (act != kActSilu && act != kActGelu) return FMOE_ERR_BAD_ARG;
   if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
@@ -1063,13 +1075,14 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
   const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
   switch (dtype) {
     case FMOE_DTYPE_F32:
-      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes, act);
+      return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes, act,
+                              raw_scores);
     case FMOE_DTYPE_BF16:
       return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes, act);
+                                      between_passes, act, raw_scores);
     case FMOE_DTYPE_F16:
       return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes, act);
+                                      between_passes, act, raw_scores);
     default:
       return FMOE_ERR_BAD_ARG;
   }
@@ -1082,7 +1095,8 @@ size_t expert_backward_workspace_bytes(int64_t T, int H, int64_t N, int k) {
 
 int launch_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
                            const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype, int64_t T,
-                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+                           int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                           const float* saved_scores) {
   if (T < 0 || H <= 0 || N <= 0 || k < 0) return FMOE_ERR_BAD_ARG;
   if (dx == nullptr || ddown == nullptr || dup == nullptr) return FMOE_ERR_BAD_ARG;
   if (N > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
@@ -1104,12 +1118,14 @@ int launch_expert_backward(const void* dout, const void* x, const void* down, co
   if (ws == nullptr || ws_bytes < w.bytes) return FMOE_ERR_WORKSPACE;
   switch (dtype) {
     case FMOE_DTYPE_F32:
-      return run_backward<float>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream);
+      return run_backward<float>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream,
+                                 saved_scores);
     case FMOE_DTYPE_BF16:
       return run_backward<__nv_bfloat16>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status,
-                                         stream);
+                                         stream, saved_scores);
     case FMOE_DTYPE_F16:
-      return run_backward<__half>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream);
+      return run_backward<__half>(dout, x, down, up, indices, gates, dx, ddown, dup, dgates, T, H, N, k, w, status, stream,
+                                  saved_scores);
     default:
       return FMOE_ERR_BAD_ARG;
   }

@@ -8,7 +8,7 @@ from .. import _lib
 from .utils import contiguous
 
 
-def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, out_dtype=None):
+def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, out_dtype=None, save_scores=False):
     dev = _lib.require_cuda(hidden_states, down_weights, up_weights, indices, routing_weights)
     x, d, u, idx, g = (contiguous(t) for t in (hidden_states, down_weights, up_weights, indices, routing_weights))
     if x.dim() != 2 or d.dim() != 2 or u.dim() != 2 or idx.dim() != 2:
@@ -29,17 +29,25 @@ def _expert_forward(hidden_states, down_weights, up_weights, indices, routing_we
     L = _lib.lib()
     ws_bytes = L.fmoe_expert_workspace_bytes(T, H, N, k)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    saved = torch.empty((T, k), device=dev, dtype=torch.float32) if save_scores else None
     with torch.cuda.device(dev):
-        rc = L.fmoe_expert_forward(
-            x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), out.data_ptr(),
-            _lib.dtype_code(x), _lib.DTYPE_CODE[out_dtype], T, H, N, k, ws.data_ptr(), ws_bytes,
-            _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
-        )
+        if save_scores:
+            rc = L.fmoe_expert_forward_saving_scores(
+                x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), out.data_ptr(), saved.data_ptr(),
+                _lib.dtype_code(x), _lib.DTYPE_CODE[out_dtype], T, H, N, k, ws.data_ptr(), ws_bytes,
+                _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+            )
+        else:
+            rc = L.fmoe_expert_forward(
+                x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), out.data_ptr(),
+                _lib.dtype_code(x), _lib.DTYPE_CODE[out_dtype], T, H, N, k, ws.data_ptr(), ws_bytes,
+                _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+            )
     _lib.check(rc, "fmoe_expert_forward")
-    return out
+    return (out, saved) if save_scores else out
 
 
-def _expert_backward(dout, hidden_states, down_weights, up_weights, indices, routing_weights):
+def _expert_backward(dout, hidden_states, down_weights, up_weights, indices, routing_weights, saved_scores=None):
     """(dx, ddown, dup, dgates) of the expert sum (flash_moe/ops/triton/flash_expert.py:653-745)."""
     dev = _lib.require_cuda(dout, hidden_states, down_weights, up_weights, indices, routing_weights)
     do, x, d, u, idx, g = (contiguous(t) for t in (dout, hidden_states, down_weights, up_weights, indices, routing_weights))
@@ -57,7 +65,8 @@ def _expert_backward(dout, hidden_states, down_weights, up_weights, indices, rou
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         rc = L.fmoe_expert_backward(
-            do.data_ptr(), x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(), dx.data_ptr(),
+            do.data_ptr(), x.data_ptr(), d.data_ptr(), u.data_ptr(), idx.data_ptr(), g.data_ptr(),
+            _lib.ptr(saved_scores), dx.data_ptr(),
             dd.data_ptr(), du.data_ptr(), dg.data_ptr(), _lib.dtype_code(x), T, H, N, k, ws.data_ptr(), ws_bytes,
             _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
         )
@@ -68,13 +77,17 @@ def _expert_backward(dout, hidden_states, down_weights, up_weights, indices, rou
 class FlashExpertFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden_states, down_weights, up_weights, indices, routing_weights):
-        ctx.save_for_backward(hidden_states, down_weights, up_weights, indices, routing_weights)
-        return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights)
+        if not any(ctx.needs_input_grad):
+            return _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights)
+        # like the reference (flash_expert.py:784-794) keep the pre-activation scores for the backward
+        out, scores = _expert_forward(hidden_states, down_weights, up_weights, indices, routing_weights, save_scores=True)
+        ctx.save_for_backward(hidden_states, down_weights, up_weights, indices, routing_weights, scores)
+        return out
 
     @staticmethod
     def backward(ctx, dexperts_states):
-        x, d, u, idx, g = ctx.saved_tensors
-        dx, dd, du, dg = _expert_backward(dexperts_states, x, d, u, idx, g)
+        x, d, u, idx, g, scores = ctx.saved_tensors
+        dx, dd, du, dg = _expert_backward(dexperts_states, x, d, u, idx, g, scores)
         return dx, dd, du, None, dg.to(g.dtype)
 
 

@@ -130,18 +130,24 @@ int fmoe_pkm_forward(const void* values, const void* routing_weights, const int6
  * fmoe_router_topk_backward - flash_moe/ops/triton/flash_router.py:197-249,:316-345:
  *   dlog_probs [2, T, num_keys] (fully written): dlog_probs[0,t,i] / [1,t,j] = sum of dscores[t,s] over the slots
  *   whose index is i*num_keys + j.
- * fmoe_expert_backward - flash_moe/ops/triton/flash_expert.py:214-525,:653-745: from dout [T,H] and the
- *   forward's inputs (the scores are recomputed) dx [T,H], ddown / dup [N,H] (every row written; rows of
- *   experts nobody selected are zero), dgates [T,k].  Skipped (out-of-range) ids get zero gradient.
+ * fmoe_expert_forward_saving_scores - fmoe_expert_forward that also writes scores_out [T,k] float32, the
+ *   pre-activation scores <x[t], down[e]> the reference saves for its backward (flash_expert.py:784-794).
+ * fmoe_expert_backward - flash_moe/ops/triton/flash_expert.py:214-525,:653-745: from dout [T,H], the forward's
+ *   inputs and saved_scores (nullable: recomputed when absent) dx [T,H], ddown / dup [N,H] (every row written;
+ *   rows of experts nobody selected are zero), dgates [T,k].  Skipped (out-of-range) ids get zero gradient.
  * fmoe_swiglu_backward - flash_moe/ops/triton/flash_mlp.py:52-102: da = dh * b * silu'(a), db = dh * silu(a)
  *   over num_elements values (a multiple of 16 bytes); h (nullable) receives silu(a) * b.
  */
 int fmoe_router_topk_backward(const void* dscores, const int64_t* indices, int dtype, int64_t num_tokens, int num_keys,
                               int top_k, void* dlog_probs, fmoe_stream_t stream);
+int fmoe_expert_forward_saving_scores(const void* x, const void* down, const void* up, const int64_t* indices,
+                                      const void* gates, void* out, float* scores_out, int dtype, int out_dtype,
+                                      int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                                      size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 size_t fmoe_expert_backward_workspace_bytes(int64_t num_tokens, int hidden, int64_t num_experts, int top_k);
 int fmoe_expert_backward(const void* dout, const void* x, const void* down, const void* up, const int64_t* indices,
-                         const void* gates, void* dx, void* ddown, void* dup, void* dgates, int dtype,
-                         int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
+                         const void* gates, const float* saved_scores, void* dx, void* ddown, void* dup, void* dgates,
+                         int dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k, void* workspace,
                          size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
                          int64_t num_elements, fmoe_stream_t stream);
