@@ -19,6 +19,7 @@ DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 NUM_STAGES = 6
 STAGE_NAMES = ("router_front", "router_topk", "expert_scores", "expert_accum", "mlp_up", "mlp_down")
 
+ERR_UNSUPPORTED = 2  # fmoe_error: a shape/dtype combination no kernel covers
 STATUS_BAD_EXPERT_ID = 1
 STATUS_WAIT_TIMEOUT = 2
 STATUS_BAD_ROW_INDEX = 4
@@ -84,6 +85,7 @@ SIGNATURES = {
     "fmoe_peer_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_pkm_workspace_bytes": (_Z, [_L, _I]),
     "fmoe_pkm_forward": (_I, [_P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
+    "fmoe_mlp_forward_saving_preacts": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_router_topk_backward": (_I, [_P, _P, _I, _L, _I, _I, _P, _P]),
     "fmoe_expert_backward_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward_saving_scores": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),

@@ -89,9 +89,11 @@ int router_front(const void* x, const void* w, void* rm, void* rv, int training,
 size_t mlp_ws(int64_t T, int I, int dtype) { return align_up(static_cast<size_t>(T) * I * dtype_size(dtype), 256); }
 
 int mlp_up(const void* x, const void* gw, const void* uw, void* h, int dtype, int64_t T, int H, int I, int32_t* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, void* pre_gate = nullptr, void* pre_up = nullptr) {
   const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(x) && aligned16(gw) && aligned16(uw);
-  if (tc && gemm_pair_supported(T, I, H)) return launch_gemm_swiglu_pair(x, gw, uw, h, dtype, T, I, H, status, stream);
+  if (tc && gemm_pair_supported(T, I, H))
+    return launch_gemm_swiglu_pair(x, gw, uw, h, dtype, T, I, H, status, stream, pre_gate, pre_up);
+  if (pre_gate != nullptr || pre_up != nullptr) return FMOE_ERR_UNSUPPORTED;  // only the CTA-pair kernel keeps them
   if (tc) return launch_gemm_swiglu(x, gw, uw, h, dtype, T, I, H, status, stream);
   return launch_simt_gemm(x, H, gw, uw, nullptr, h, I, dtype, 1, T, I, H, stream);
 }
@@ -290,6 +292,23 @@ int fmoe_mlp_forward(const void* x, const void* gate_w, const void* up_w, const 
   int rc = mlp_up(x, gate_w, up_w, workspace, dtype, num_tokens, hidden, intermediate, status, s);
   if (rc != FMOE_OK) return rc;
   return mlp_down(workspace, down_w, addend, out, dtype, num_tokens, hidden, intermediate, status, s);
+}
+
+int fmoe_mlp_forward_saving_preacts(const void* x, const void* gate_w, const void* up_w, const void* down_w,
+                                    void* out, void* pre_gate, void* pre_up, int dtype, int64_t num_tokens, int hidden,
+                                    int intermediate, void* workspace, size_t workspace_bytes, int32_t* status,
+                                    fmoe_stream_t stream) {
+  if (!valid_dtype(dtype) || num_tokens < 0 || hidden <= 0 || intermediate <= 0) return FMOE_ERR_BAD_ARG;
+  if (num_tokens == 0) return FMOE_OK;
+  if (x == nullptr || gate_w == nullptr || up_w == nullptr || down_w == nullptr || out == nullptr || pre_gate == nullptr ||
+      pre_up == nullptr)
+    return FMOE_ERR_BAD_ARG;
+  if (!aligned16(pre_gate) || !aligned16(pre_up)) return FMOE_ERR_ALIGNMENT;
+  if (workspace == nullptr || workspace_bytes < mlp_ws(num_tokens, intermediate, dtype)) return FMOE_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = mlp_up(x, gate_w, up_w, workspace, dtype, num_tokens, hidden, intermediate, status, s, pre_gate, pre_up);
+  if (rc != FMOE_OK) return rc;
+  return mlp_down(workspace, down_w, nullptr, out, dtype, num_tokens, hidden, intermediate, status, s);
 }
 
 size_t fmoe_layer_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int64_t num_experts, int num_keys,

@@ -146,7 +146,8 @@ bool gemm_router_fused_supported(int nk);
 // CTA-pair (cta_group::2) versions of the two shared-MLP GEMMs (gemm_sm100_pair.cu)
 bool gemm_pair_supported(int64_t M, int N, int K);
 int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I,
-                            int K, int32_t* status, cudaStream_t stream);
+                            int K, int32_t* status, cudaStream_t stream, void* pre_gate = nullptr,
+                            void* pre_up = nullptr);
 int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N,
                          int K, int32_t* status, cudaStream_t stream);
 

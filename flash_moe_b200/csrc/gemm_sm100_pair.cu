@@ -44,6 +44,8 @@ struct PairEpi {
   const float* addend;
   int64_t ldo;
   int n_valid;
+  void* pre_gate;  // SWIGLU only, nullable: x Wg^T and x Wu^T rounded to T, kept for the backward pass
+  void* pre_up;
 };
 
 template <typename T> struct UmmaFmt;
@@ -176,6 +178,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
       if constexpr (EPI == PAIR_EPI_SWIGLU) {
         T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
+        T* grow = ep.pre_gate != nullptr ? static_cast<T*>(ep.pre_gate) + row * ep.ldo : nullptr;
+        T* urow = ep.pre_up != nullptr ? static_cast<T*>(ep.pre_up) + row * ep.ldo : nullptr;
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / 64; ++c) {
           uint32_t g[32], u[32];
@@ -190,7 +194,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 f[i] = silu_f32(__uint_as_float(g[v * 8 + i])) * __uint_as_float(u[v * 8 + i]);
-              if (col0 + v * 8 < ep.n_valid) *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
+              if (col0 + v * 8 < ep.n_valid) {
+                *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
+                if (grow != nullptr) {
+                  float fg[8], fu[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    fg[i] = __uint_as_float(g[v * 8 + i]);
+                    fu[i] = __uint_as_float(u[v * 8 + i]);
+                  }
+                  *reinterpret_cast<uint4*>(grow + col0 + v * 8) = pack16<T>(fg);
+                  *reinterpret_cast<uint4*>(urow + col0 + v * 8) = pack16<T>(fu);
+                }
+              }
             }
           }
         }
@@ -314,13 +330,14 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB0, const CUtensorMap
 bool gemm_pair_supported(int64_t M, int N, int K) { return M >= 512 && N >= 256 && K >= 256; }
 
 int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I,
-                            int K, int32_t* status, cudaStream_t stream) {
+                            int K, int32_t* status, cudaStream_t stream, void* pre_gate, void* pre_up) {
   CUtensorMap tA, tG, tU;
   int rc;
   if ((rc = make_map(&tA, x, dtype, K, M, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_map(&tG, gate_w, dtype, K, I, BLOCK_N / 2)) != FMOE_OK) return rc;
   if ((rc = make_map(&tU, up_w, dtype, K, I, BLOCK_N / 2)) != FMOE_OK) return rc;
-  PairEpi ep{h, nullptr, I, I};
+  if ((pre_gate == nullptr) != (pre_up == nullptr)) return FMOE_ERR_BAD_ARG;
+  PairEpi ep{h, nullptr, I, I, pre_gate, pre_up};
   const int n_tiles = (I + 127) / 128;
   if (dtype == FMOE_DTYPE_BF16)
     return launch_pair<PAIR_EPI_SWIGLU, __nv_bfloat16>(tA, tG, tU, ep, M, n_tiles, K, status, stream);
@@ -333,7 +350,7 @@ int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void
   int rc;
   if ((rc = make_map(&tA, a, dtype, K, M, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_map(&tB, b, dtype, K, N, BLOCK_N / 2)) != FMOE_OK) return rc;
-  PairEpi ep{out, addend, N, N};
+  PairEpi ep{out, addend, N, N, nullptr, nullptr};
   const int n_tiles = (N + 255) / 256;
   if (dtype == FMOE_DTYPE_BF16)
     return launch_pair<PAIR_EPI_ADD, __nv_bfloat16>(tA, tB, tB, ep, M, n_tiles, K, status, stream);

@@ -8,7 +8,7 @@ from .. import _lib
 from .utils import contiguous
 
 
-def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None):
+def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None, save_preacts=False):
     dev = _lib.require_cuda(x, gate_weight, up_weight, down_weight, addend)
     lead = x.shape[:-1]
     H = x.shape[-1]
@@ -28,13 +28,26 @@ def _mlp_forward(x, gate_weight, up_weight, down_weight, addend=None):
     code = _lib.dtype_code(x2)
     ws_bytes = L.fmoe_mlp_workspace_bytes(T, H, I, code)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    if save_preacts and addend is None and T > 0:
+        # the fused gate/up GEMM can also store the two pre-activations (its CTA-pair form only)
+        a = torch.empty((T, I), device=dev, dtype=x2.dtype)
+        b = torch.empty((T, I), device=dev, dtype=x2.dtype)
+        with torch.cuda.device(dev):
+            rc = L.fmoe_mlp_forward_saving_preacts(
+                x2.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), code,
+                T, H, I, ws.data_ptr(), ws_bytes, _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
+            )
+        if rc == 0:
+            return out.view(*lead, H), a, b
+        if rc != _lib.ERR_UNSUPPORTED:
+            _lib.check(rc, "fmoe_mlp_forward_saving_preacts")
     with torch.cuda.device(dev):
         rc = L.fmoe_mlp_forward(
             x2.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), _lib.ptr(addend), out.data_ptr(), code, T, H, I,
             ws.data_ptr(), ws_bytes, _lib.status_word(dev).data_ptr(), _lib.current_stream_ptr(dev),
         )
     _lib.check(rc, "fmoe_mlp_forward")
-    return out.view(*lead, H)
+    return (out.view(*lead, H), None, None) if save_preacts else out.view(*lead, H)
 
 
 def swiglu_backward(dh, a, b, want_h=False):
@@ -54,22 +67,34 @@ def swiglu_backward(dh, a, b, want_h=False):
 
 class FlashMLPFunc(torch.autograd.Function):
     """Forward: the fused kernels.  Backward: like the reference (flash_mlp.py:150-181) the contractions are plain
-    library GEMMs (torch.matmul); the two pre-activations are recomputed instead of saved, the SwiGLU derivative
-    is this library's kernel."""
+    library GEMMs (torch.matmul) and the SwiGLU derivative is this library's kernel.  The two pre-activations are
+    kept by the forward when the fused GEMM can store them (as the reference's TritonSwiGLUFunc does) and
+    recomputed otherwise."""
 
     @staticmethod
     def forward(ctx, x, gate_weight, up_weight, down_weight):
-        ctx.save_for_backward(x, gate_weight, up_weight, down_weight)
-        return _mlp_forward(x, gate_weight, up_weight, down_weight)
+        if not any(ctx.needs_input_grad):
+            return _mlp_forward(x, gate_weight, up_weight, down_weight)
+        out, a, b = _mlp_forward(x, gate_weight, up_weight, down_weight, save_preacts=True)
+        ctx.have_preacts = a is not None
+        if ctx.have_preacts:
+            ctx.save_for_backward(x, gate_weight, up_weight, down_weight, a, b)
+        else:
+            ctx.save_for_backward(x, gate_weight, up_weight, down_weight)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
-        x, wg, wu, wd = ctx.saved_tensors
+        if ctx.have_preacts:
+            x, wg, wu, wd, a, b = ctx.saved_tensors
+        else:
+            x, wg, wu, wd = ctx.saved_tensors
         H = x.shape[-1]
         x2 = x.reshape(-1, H)
         dy2 = dy.reshape(-1, H).to(x2.dtype)
-        a = torch.matmul(x2, wg.t())
-        b = torch.matmul(x2, wu.t())
+        if not ctx.have_preacts:
+            a = torch.matmul(x2, wg.t())
+            b = torch.matmul(x2, wu.t())
         dh = torch.matmul(dy2, wd)
         da, db, h = swiglu_backward(dh, a, b, want_h=True)
         dwd = torch.matmul(dy2.t(), h)

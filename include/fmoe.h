@@ -215,6 +215,17 @@ int fmoe_mlp_forward(const void* x, const void* gate_w, const void* up_w, const 
                      size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * fmoe_mlp_forward that also keeps the two pre-activations pre_gate = x Wg^T and pre_up = x Wu^T ([T, I] of `dtype`),
+ * the tensors the reference's TritonSwiGLUFunc saves for its backward (flash_moe/ops/triton/flash_mlp.py:150-156).
+ * They are written by the epilogue of the fused gate/up GEMM, which only its CTA-pair form supports: 16-bit dtypes,
+ * T >= 512, I >= 256, H >= 256 - other shapes return FMOE_ERR_UNSUPPORTED (callers then recompute in the backward).
+ */
+int fmoe_mlp_forward_saving_preacts(const void* x, const void* gate_w, const void* up_w, const void* down_w,
+                                    void* out, void* pre_gate, void* pre_up, int dtype, int64_t num_tokens, int hidden,
+                                    int intermediate, void* workspace, size_t workspace_bytes, int32_t* status,
+                                    fmoe_stream_t stream);
+
+/*
  * Whole layer forward.  Replaces FlashMoE.forward, flash_moe/modules/flash_moe.py:55-105.
  * Parameter names follow the module: gate_proj/up_proj [I,H], down_proj [H,I], router_gate
  * [2*num_keys, H], down_embed/up_embed [N, H], router_norm running buffers [H].

@@ -239,3 +239,23 @@ def test_backward_with_no_pairs():
     torch.cuda.synchronize()
     assert float(dx.abs().max()) == 0.0 and float(dd.abs().max()) == 0.0 and float(du.abs().max()) == 0.0
     assert dg.shape == (6, 0)
+
+
+def test_mlp_backward_with_kept_preactivations():
+    """A shape the CTA-pair GEMM covers: the forward keeps x Wg^T and x Wu^T, the backward uses them."""
+    from flash_moe_b200.ops.flash_mlp import FlashMLPFunc, _mlp_forward
+
+    dtype = torch.bfloat16
+    T, H, I = 1024, 256, 512
+    x = (randn((T, H), 1, torch.float32) * 0.5).to(dtype)
+    wg, wu = ((randn((I, H), s, torch.float32) * 0.1).to(dtype) for s in (2, 3))
+    wd = (randn((H, I), 4, torch.float32) * 0.1).to(dtype)
+    dy = randn((T, H), 5, torch.float32).to(dtype)
+    out, a, b = _mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), save_preacts=True)
+    assert a is not None and rel_err(a, x.float() @ wg.float().t()) < 1e-2 and rel_err(b, x.float() @ wu.float().t()) < 1e-2
+    assert torch.equal(out, _mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda()))  # same kernels, same output
+    leaves = [t.cuda().requires_grad_() for t in (x, wg, wu, wd)]
+    FlashMLPFunc.apply(*leaves).backward(dy.cuda())
+    want = O.mlp_backward(dy, x, wg, wu, wd)
+    for leaf, w_ in zip(leaves, want):
+        assert rel_err(leaf.grad, w_) <= 2e-2
