@@ -91,7 +91,7 @@ SIGNATURES = {
     "fmoe_expert_forward_saving_scores": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_expert_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_swiglu_backward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _P]),
-    "fmoe_gather_probe": (_I, [_P, _P, _L, _I, _I, _P, _P]),
+    "fmoe_gather_probe": (_I, [_P, _L, _P, _L, _I, _I, _I, _P, _P, _P]),
     "fmoe_combine_partial_rows": (_I, [_P, _L, _P, _I, _L, _I, _P, _P, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),

@@ -17,7 +17,9 @@ from . import _lib
 
 
 def measure_gather_roof(device, row_bytes: int = 2048, rows: int = 16384, count: int = 262144, reps: int = 5):
-    """Best gathered-row rate in GB/s over a few grid sizes, and the per-grid results."""
+    """Best gathered-row rate in GB/s over the probe's variants, and the per-variant results: register loads at a
+    few grid sizes, bulk copies and 16-byte cp.async copies into a shared-memory ring (the latter is how the fused expert
+    kernel fetches its rows)."""
     dev = torch.device(device)
     table = torch.ones(rows * row_bytes, dtype=torch.uint8, device=dev)
     ids = torch.randint(0, rows, (count,), device=dev, dtype=torch.int32, generator=torch.Generator(device=dev).manual_seed(1))
@@ -26,18 +28,24 @@ def measure_gather_roof(device, row_bytes: int = 2048, rows: int = 16384, count:
     results = {}
     with torch.cuda.device(dev):
         stream = _lib.current_stream_ptr(dev)
-        for ctas in (4, 8, 12, 16):
+        status = _lib.status_word(dev).data_ptr()
+        for name, ctas, mode in (("4_ctas_per_sm", 4, 0), ("8_ctas_per_sm", 8, 0), ("12_ctas_per_sm", 12, 0),
+                                 ("16_ctas_per_sm", 16, 0), ("bulk_ring", 1, 1), ("cp_async_ring", 1, 2)):
             best = None
             for _ in range(reps):
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                _lib.check(L.fmoe_gather_probe(table.data_ptr(), ids.data_ptr(), count, row_bytes, ctas, sink.data_ptr(), stream),
-                           "fmoe_gather_probe")
+                rc = L.fmoe_gather_probe(table.data_ptr(), rows, ids.data_ptr(), count, row_bytes, ctas, mode,
+                                         sink.data_ptr(), status, stream)
+                if rc == _lib.ERR_UNSUPPORTED:  # this row size does not fit this variant's ring
+                    break
+                _lib.check(rc, "fmoe_gather_probe")
                 b.record()
                 torch.cuda.synchronize(dev)
                 ms = a.elapsed_time(b)
                 best = ms if best is None else min(best, ms)
-            results[f"{ctas}_ctas_per_sm"] = round(count * row_bytes / (best * 1e-3) / 1e9, 1)
+            if best is not None:
+                results[name] = round(count * row_bytes / (best * 1e-3) / 1e9, 1)
     return max(results.values()), results
 
 

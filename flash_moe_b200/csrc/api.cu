@@ -9,6 +9,7 @@ int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, in
               int dtype, int64_t ntok, int H, float* ws, const float* global_sums, int64_t global_count,
               cudaStream_t stream);
 int launch_bn_sums(const void* x, int dtype, int64_t ntok, int H, float* ws, float* sums, cudaStream_t stream);
+void bn_stats_in_workspace(float* ws, int H, const float** mean, const float** invstd);
 
 int device_sm_count() {
   static int cache[64] = {0};
@@ -71,9 +72,23 @@ int router_front(const void* x, const void* w, void* rm, void* rv, int training,
   Carver c(ws);
   void* xn = c.take(static_cast<size_t>(T) * H * dtype_size(dtype));
   float* bnws = static_cast<float*>(c.take(bn_workspace_bytes(H)));
-  int rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, bn_sums, bn_count, stream);
-  if (rc != FMOE_OK) return rc;
   const bool tc = is16(dtype) && (H % 8 == 0) && aligned16(w);
+  int rc;
+  if (logp == nullptr && tc && aligned16(x) && aligned16(logits) && router_bn_gemm_supported(dtype, T, 2 * nk, H)) {
+    // one kernel: the GEMM normalises its x tiles in shared memory (training: after the statistics pre-pass)
+    const float *mean = nullptr, *invstd = nullptr;
+    if (training) {
+      rc = launch_bn(x, nullptr, rm, rv, training, momentum, eps, dtype, T, H, bnws, bn_sums, bn_count, stream);
+      if (rc != FMOE_OK) return rc;
+      bn_stats_in_workspace(bnws, H, &mean, &invstd);
+    } else if (rm == nullptr || rv == nullptr) {
+      return FMOE_ERR_BAD_ARG;
+    }
+    return launch_router_bn_gemm(x, w, mean, invstd, training ? nullptr : rm, training ? nullptr : rv, eps, logits, dtype,
+                                 T, 2 * nk, H, status, stream);
+  }
+  rc = launch_bn(x, xn, rm, rv, training, momentum, eps, dtype, T, H, bnws, bn_sums, bn_count, stream);
+  if (rc != FMOE_OK) return rc;
   if (logp != nullptr && tc && gemm_router_fused_supported(nk) && aligned16(logits) && aligned16(logp))
     return launch_gemm_router(xn, H, 0, w, logits, logp, dtype, T, nk, H, status, stream);
   if (tc && (2 * nk) % 8 == 0 && aligned16(logits))
@@ -251,9 +266,10 @@ int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da,
   return launch_swiglu_backward(dh, a, b, da, db, h, dtype, num_elements, static_cast<cudaStream_t>(stream));
 }
 
-int fmoe_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
-                      float* sink, fmoe_stream_t stream) {
-  return launch_gather_probe(table, row_ids, count, row_bytes, ctas_per_sm, sink, static_cast<cudaStream_t>(stream));
+int fmoe_gather_probe(const void* table, int64_t num_rows, const int32_t* row_ids, int64_t count, int row_bytes,
+                      int ctas_per_sm, int mode, float* sink, int32_t* status, fmoe_stream_t stream) {
+  return launch_gather_probe(table, num_rows, row_ids, count, row_bytes, ctas_per_sm, mode, sink, status,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,

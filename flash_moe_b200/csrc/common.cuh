@@ -122,6 +122,11 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
                           size_t ws_bytes, int32_t* status, cudaStream_t stream, void* const* between_passes = nullptr,
                           int act = 0, float* raw_scores = nullptr);
 // raw_scores (nullable) [T, k] float32 receives <x[t], down[e]> before the activation, for the backward pass.
+// both steps in one kernel for 16-bit tables (expert_fused.cu): rows streamed through a shared-memory ring
+bool expert_fused_supported(int dtype, int64_t T, int H, int k);
+int launch_expert_fused(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates,
+                        void* out, int dtype, int out_f32, int64_t T, int H, int64_t N, int k, int act,
+                        float* raw_scores, int32_t* status, cudaStream_t stream);
 // the same sum with both tables sharded by e % world over the GPUs of a node; *_shards are DEVICE arrays of `world`
 // row-0 pointers (peer pointers for the other GPUs); 16-bit dtypes only
 int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
@@ -143,6 +148,11 @@ int launch_gemm_add(const void* a, const void* b, const float* addend, void* out
 int launch_gemm_router(const void* xn, int64_t a_cols, int a_half_koff, const void* w, void* logits, void* log_probs,
                        int dtype, int64_t M, int nk, int K, int32_t* status, cudaStream_t stream);
 bool gemm_router_fused_supported(int nk);
+// logits = T(batch_norm(x)) * W^T with the normalisation applied to the x tiles in shared memory (gemm_router_bn.cu)
+bool router_bn_gemm_supported(int dtype, int64_t M, int N, int K);
+int launch_router_bn_gemm(const void* x, const void* w, const float* mean, const float* invstd,
+                          const void* running_mean, const void* running_var, float eps, void* logits, int dtype,
+                          int64_t M, int N, int K, int32_t* status, cudaStream_t stream);
 // CTA-pair (cta_group::2) versions of the two shared-MLP GEMMs (gemm_sm100_pair.cu)
 bool gemm_pair_supported(int64_t M, int N, int K);
 int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I,
@@ -166,8 +176,8 @@ int launch_router_topk_backward(const void* dscores, const int64_t* indices, int
                                 void* dlog_probs, cudaStream_t stream);
 int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
                            int64_t n, cudaStream_t stream);
-int launch_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
-                        float* sink, cudaStream_t stream);
+int launch_gather_probe(const void* table, int64_t num_rows, const int32_t* row_ids, int64_t count, int row_bytes,
+                        int ctas_per_sm, int mode, float* sink, int32_t* status, cudaStream_t stream);
 int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
                         float* out, int32_t* status, cudaStream_t stream);
 

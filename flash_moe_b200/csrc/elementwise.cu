@@ -168,6 +168,7 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
         global_sums != nullptr ? global_count : ntok, H, mean, invstd, global_sums);
     FMOE_LAUNCH_CHECK();
   }
+  if (xn == nullptr) return FMOE_OK;  // statistics only: the caller normalises inside its GEMM
   constexpr int VEC = Vec16<T>::N;
   const int hv = H / VEC;
   const int gx = (hv + 127) / 128;
@@ -180,33 +181,6 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
       training ? nullptr : static_cast<const T*>(rv), eps, ntok, H);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
-}
-
-// Load-only probe of the gather pattern of the expert passes: each warp fetches batches of 4 random rows of
-// C x 512 bytes with 16-byte loads (4 x C loads per lane in flight) and folds them into a checksum.  Its rate is
-// the practical ceiling for any kernel that has to bring one table row per (token, expert) pair to an SM.
-template <int C>
-__global__ void __launch_bounds__(128) gather_probe_kernel(const uint4* __restrict__ table,
-                                                           const int32_t* __restrict__ ids, int64_t count, int row_u4,
-                                                           float* sink) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  uint32_t acc = 0;
-  for (int64_t r0 = warp_global * 4; r0 + 4 <= count; r0 += warps_total * 4) {
-    uint4 q[4][C];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint4* row = table + static_cast<int64_t>(ids[r0 + u]) * row_u4;
-#pragma unroll
-      for (int c = 0; c < C; ++c) q[u][c] = __ldg(row + c * 32 + lane);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int c = 0; c < C; ++c) acc += q[u][c].x ^ q[u][c].y ^ q[u][c].z ^ q[u][c].w;
-  }
-  if (acc == 0x12345u && sink != nullptr) sink[0] = static_cast<float>(acc);  // keeps the loads alive
 }
 
 // out[t] = sum over sources g of rows[slot[g * ntok + t]] (slot < 0: source g holds nothing for token t).
@@ -244,6 +218,12 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const float4* __restr
 
 size_t bn_workspace_bytes(int H) { return static_cast<size_t>(2 * kBnSplits + 2) * H * sizeof(float); }
 
+// where launch_bn leaves the per-feature mean and inverse standard deviation of a training-mode batch (float32 [H])
+void bn_stats_in_workspace(float* ws, int H, const float** mean, const float** invstd) {
+  *mean = ws + static_cast<size_t>(2 * kBnSplits) * H;
+  *invstd = *mean + H;
+}
+
 // per-feature sum and sum of squares of this rank's rows: sums[0:H], sums[H:2H] (float32)
 int launch_bn_sums(const void* x, int dtype, int64_t ntok, int H, float* ws, float* sums, cudaStream_t stream) {
   if (x == nullptr || ws == nullptr || sums == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
@@ -265,9 +245,9 @@ int launch_bn_sums(const void* x, int dtype, int64_t ntok, int H, float* ws, flo
 int launch_bn(const void* x, void* xn, void* running_mean, void* running_var, int training, float momentum, float eps,
               int dtype, int64_t ntok, int H, float* ws, const float* global_sums, int64_t global_count,
               cudaStream_t stream) {
-  if (x == nullptr || xn == nullptr || ws == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
+  if (x == nullptr || ws == nullptr || ntok <= 0 || H <= 0) return FMOE_ERR_BAD_ARG;
   if (!training && (running_mean == nullptr || running_var == nullptr)) return FMOE_ERR_BAD_ARG;
-  if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(x) || !aligned16(xn)) return FMOE_ERR_ALIGNMENT;
+  if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(x) || (xn != nullptr && !aligned16(xn))) return FMOE_ERR_ALIGNMENT;
   switch (dtype) {
     case FMOE_DTYPE_F32: return bn_typed<float>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, global_sums, global_count, stream);
     case FMOE_DTYPE_BF16: return bn_typed<__nv_bfloat16>(x, xn, running_mean, running_var, training, momentum, eps, ntok, H, ws, global_sums, global_count, stream);
@@ -310,23 +290,6 @@ int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot
   const int grid = static_cast<int>(want < cap ? want : cap);
   combine_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(rows), num_rows, slot, num_sources, ntok,
                                                 h4, reinterpret_cast<float4*>(out), status);
-  FMOE_LAUNCH_CHECK();
-  return FMOE_OK;
-}
-
-int launch_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
-                        float* sink, cudaStream_t stream) {
-  if (table == nullptr || row_ids == nullptr || count < 0 || ctas_per_sm < 1 || ctas_per_sm > 32) return FMOE_ERR_BAD_ARG;
-  if (row_bytes % 512 != 0 || !aligned16(table)) return FMOE_ERR_ALIGNMENT;
-  const int grid = device_sm_count() * ctas_per_sm;
-  const uint4* t = static_cast<const uint4*>(table);
-  switch (row_bytes / 512) {
-    case 1: gather_probe_kernel<1><<<grid, 128, 0, stream>>>(t, row_ids, count, row_bytes / 16, sink); break;
-    case 2: gather_probe_kernel<2><<<grid, 128, 0, stream>>>(t, row_ids, count, row_bytes / 16, sink); break;
-    case 4: gather_probe_kernel<4><<<grid, 128, 0, stream>>>(t, row_ids, count, row_bytes / 16, sink); break;
-    case 8: gather_probe_kernel<8><<<grid, 128, 0, stream>>>(t, row_ids, count, row_bytes / 16, sink); break;
-    default: return FMOE_ERR_UNSUPPORTED;
-  }
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }

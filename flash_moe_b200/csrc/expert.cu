@@ -525,14 +525,20 @@ void launch_accum(const void* up, const int64_t* idx, const float* gs, void* out
 // 16-bit tables are gathered per token (no sort, tensor-core dot products) whatever their size: measured against
 // the expert-centric order at 2^16 experts x 131072 tokens (3.07 vs 3.94 ms) and at 2^20 experts with Zipf ids
 // (0.54 vs 0.83 ms; uniform ids 1.23 vs 1.16 ms).  float32 takes the expert-centric order.
-template <typename T> bool use_token_centric(int64_t N, int H) {
-  if (sizeof(T) != 2) return false;
-  static const int forced = [] {  // debugging aid: FMOE_EXPERT_SCHEDULE=token|sorted overrides the size rule
+// debugging / measurement aid: FMOE_EXPERT_SCHEDULE=token|sorted|fused forces one schedule for 16-bit tables (read
+// once per process; `fused` only where that kernel applies); anything else leaves the default choice
+int forced_schedule() {
+  static const int forced = [] {
     const char* v = std::getenv("FMOE_EXPERT_SCHEDULE");
     if (v == nullptr) return 0;
-    return v[0] == 't' ? 1 : (v[0] == 's' ? 2 : 0);
+    return v[0] == 't' ? 1 : (v[0] == 's' ? 2 : (v[0] == 'f' ? 3 : 0));
   }();
-  if (forced != 0) return forced == 1;
+  return forced;
+}
+
+template <typename T> bool use_token_centric(int64_t N, int H) {
+  if (sizeof(T) != 2) return false;
+  if (forced_schedule() == 1 || forced_schedule() == 2) return forced_schedule() == 1;
   (void)N;
   (void)H;
   return true;
@@ -629,12 +635,28 @@ int run_accum(const void* table, const int64_t* idx, const float* coef, void* ou
 template <typename T>
 int run_typed(const void* x, const void* down, const void* up, const int64_t* idx, const void* gates, void* out,
               int out_f32, int64_t T_, int H, int64_t N, int k, const ExpertWs& w, int32_t* status,
-              cudaStream_t stream, void* const* between_passes, int act, float* raw_scores) {
+              cudaStream_t stream, void* const* between_passes, int act, float* raw_scores, int dtype) {
+  auto mark_between = [&]() -> int {
+    if (between_passes != nullptr)
+      for (int i = 0; i < 2; ++i)
+        if (between_passes[i] != nullptr)
+          FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(between_passes[i]), stream));
+    return FMOE_OK;
+  };
+  // The fused kernel pays off once the tables are far larger than L2 (its deep ring of asynchronous copies covers
+  // the DRAM latency: 0.71 vs 0.93 ms at 2^20 experts x 2048); while they sit in L2 the two passes are faster
+  // (110 vs 162 us at 2^14 experts x 1024), so tables below 1 GiB each take the two-pass path.
+  const bool big_tables = static_cast<double>(N) * H * sizeof(T) >= 1073741824.0;
+  const bool want_fused = forced_schedule() == 3 || (forced_schedule() == 0 && big_tables);
+  if (sizeof(T) == 2 && want_fused && expert_fused_supported(dtype, T_, H, k)) {
+    // one kernel for both steps: the marks that separate the two passes fall in front of it
+    const int rc = mark_between();
+    if (rc != FMOE_OK) return rc;
+    return launch_expert_fused(x, down, up, idx, gates, out, dtype, out_f32, T_, H, N, k, act, raw_scores, status, stream);
+  }
   int rc = run_scores<T>(x, down, idx, gates, w.gs, T_, H, N, k, w, false, status, stream, act, raw_scores);
   if (rc != FMOE_OK) return rc;
-  if (between_passes != nullptr)
-    for (int i = 0; i < 2; ++i)
-      if (between_passes[i] != nullptr) FMOE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(between_passes[i]), stream));
+  if ((rc = mark_between()) != FMOE_OK) return rc;
   return run_accum<T>(up, idx, w.gs, out, out_f32, T_, H, N, k, stream);
 }
 
@@ -1076,13 +1098,13 @@ int launch_expert_forward(const void* x, const void* down, const void* up, const
   switch (dtype) {
     case FMOE_DTYPE_F32:
       return run_typed<float>(x, down, up, indices, gates, out, 1, T, H, N, k, w, status, stream, between_passes, act,
-                              raw_scores);
+                              raw_scores, dtype);
     case FMOE_DTYPE_BF16:
       return run_typed<__nv_bfloat16>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes, act, raw_scores);
+                                      between_passes, act, raw_scores, dtype);
     case FMOE_DTYPE_F16:
-      return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream,
-                                      between_passes, act, raw_scores);
+      return run_typed<__half>(x, down, up, indices, gates, out, out_f32, T, H, N, k, w, status, stream, between_passes,
+                               act, raw_scores, dtype);
     default:
       return FMOE_ERR_BAD_ARG;
   }

@@ -153,14 +153,21 @@ int fmoe_swiglu_backward(const void* dh, const void* a, const void* b, void* da,
                          int64_t num_elements, fmoe_stream_t stream);
 
 /*
- * Measurement aid, no counterpart in the reference: a load-only kernel with the access pattern of the two expert
- * passes (random rows of `row_bytes` = 512, 1024, 2048 or 4096 bytes of `table`, ids in row_ids[count], fetched with
- * 16-byte loads by device_sms * ctas_per_sm CTAs of 128 threads).  count * row_bytes / its duration is the rate at which
- * this GPU can bring gathered rows to its SMs - the ceiling the expert kernels are measured against when the tables are
- * resident in L2.  `sink` (nullable) is one float that is never written in practice.
+ * NOT PART OF THE LAYER - a measurement aid with no counterpart in the reference, exported only so that the
+ * benchmark can state the ceiling of the expert step on the GPU it runs on.  A load-only kernel with the access
+ * pattern of that step: the rows row_ids[count] (each in [0, num_rows); others read row 0 and raise
+ * FMOE_STATUS_BAD_ROW_INDEX in *status) of `row_bytes` bytes of `table` are brought to the SMs and dropped.
+ *   mode 0: 16-byte loads into registers by device_sms * ctas_per_sm CTAs of 128 threads (row_bytes = 512, 1024,
+ *           2048 or 4096);
+ *   mode 1: one bulk asynchronous copy per row into a shared-memory ring, one CTA per SM (row_bytes a multiple of
+ *           16 up to 6144; ctas_per_sm ignored);
+ *   mode 2: the same ring filled with 16-byte cp.async copies by four producer warps - the way the fused expert
+ *           kernel fetches its rows (row_bytes = 512, 1024 or 2048).
+ * count * row_bytes / duration is the rate at which this GPU can bring gathered rows to its SMs.  `sink` (nullable)
+ * is one float that is never written in practice.
  */
-int fmoe_gather_probe(const void* table, const int32_t* row_ids, int64_t count, int row_bytes, int ctas_per_sm,
-                      float* sink, fmoe_stream_t stream);
+int fmoe_gather_probe(const void* table, int64_t num_rows, const int32_t* row_ids, int64_t count, int row_bytes,
+                      int ctas_per_sm, int mode, float* sink, int32_t* status, fmoe_stream_t stream);
 
 /*
  * Combine step of the expert-sharded layout (tables split over GPUs by expert id, token rows sent to

@@ -173,11 +173,22 @@ def test_gather_roof_probe_runs_and_rejects_bad_rows():
     from flash_moe_b200.bench_gather_roof import measure_gather_roof
 
     best, per_grid = measure_gather_roof("cuda:0", row_bytes=1024, rows=4096, count=65536, reps=2)
-    assert best > 100.0 and len(per_grid) == 4  # GB/s; any working GPU is far above this
+    assert best > 100.0 and len(per_grid) == 6  # GB/s; any working GPU is far above this
+    assert per_grid["bulk_ring"] > 100.0 and per_grid["cp_async_ring"] > 100.0
+    _lib.read_status()
     t = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     ids = torch.zeros(8, dtype=torch.int32, device="cuda")
-    rc = _lib.lib().fmoe_gather_probe(t.data_ptr(), ids.data_ptr(), 8, 768, 4, None, _lib.current_stream_ptr(t.device))
-    assert rc == 4  # FMOE_ERR_ALIGNMENT: rows must be multiples of 512 bytes
+    L, st, stream = _lib.lib(), _lib.status_word(t.device).data_ptr(), _lib.current_stream_ptr(t.device)
+    rc = L.fmoe_gather_probe(t.data_ptr(), 4, ids.data_ptr(), 8, 768, 4, 0, None, st, stream)
+    assert rc == 4  # FMOE_ERR_ALIGNMENT: register-load rows must be multiples of 512 bytes
+    # a row id outside the table is not followed: row 0 is read instead and the status word says so
+    for mode in (0, 1, 2):
+        ids = torch.tensor([0, 1, 2, 3, 1 << 20, -5, 2, 1], dtype=torch.int32, device="cuda")
+        assert L.fmoe_gather_probe(t.data_ptr(), 8, ids.data_ptr(), 8, 512, 4, mode, None, st, stream) == 0
+        assert _lib.read_status() == _lib.STATUS_BAD_ROW_INDEX
+        ids = torch.tensor([0, 1, 2, 3, 7, 6, 2, 1], dtype=torch.int32, device="cuda")
+        assert L.fmoe_gather_probe(t.data_ptr(), 8, ids.data_ptr(), 8, 512, 4, mode, None, st, stream) == 0
+        assert _lib.read_status() == 0
 
 
 def test_empty_inputs():
