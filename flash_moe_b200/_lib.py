@@ -63,6 +63,7 @@ class LayerArgs(ctypes.Structure):
         ("bn_eps", ctypes.c_float),
         ("bn_global_sums", ctypes.c_void_p),
         ("bn_global_count", ctypes.c_int64),
+        ("residual", ctypes.c_void_p),
     ]
 
 
@@ -81,7 +82,7 @@ SIGNATURES = {
     "fmoe_router_front": (_I, [_P, _P, _P, _P, _I, _F, _F, _P, _P, _I, _L, _I, _I, _P, _Z, _P, _P]),
     "fmoe_bn_batch_sums_workspace_bytes": (_Z, [_I]),
     "fmoe_bn_batch_sums": (_I, [_P, _I, _L, _I, _P, _P, _Z, _P]),
-    "fmoe_expert_forward_sharded": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
+    "fmoe_expert_forward_sharded": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P, _P, _P, _L]),
     "fmoe_peer_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_pkm_workspace_bytes": (_Z, [_L, _I]),
     "fmoe_pkm_forward": (_I, [_P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
@@ -92,6 +93,7 @@ SIGNATURES = {
     "fmoe_expert_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_swiglu_backward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _P]),
     "fmoe_gather_probe": (_I, [_P, _L, _P, _L, _I, _I, _I, _P, _P, _P]),
+    "fmoe_selftest_wait_timeout": (_I, [ctypes.c_uint64, _P, _P, _P]),
     "fmoe_combine_partial_rows": (_I, [_P, _L, _P, _I, _L, _I, _P, _P, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),
     "fmoe_expert_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),

@@ -12,8 +12,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libfmoe_sm100a.so")
-SOURCES = ["api.cu", "router_topk.cu", "expert.cu", "expert_fused.cu", "gemm_sm100.cu", "gemm_sm100_pair.cu", "gemm_router_bn.cu", "simt_gemm.cu", "elementwise.cu", "gather_probe.cu", "backward.cu", "noalloc.cu"]
-HEADERS = ["common.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "fmoe.h")]
+SOURCES = ["api.cu", "router_topk.cu", "expert.cu", "expert_fused.cu", "gemm_sm100.cu", "gemm_sm100_pair.cu", "gemm_router_bn.cu", "simt_gemm.cu", "elementwise.cu", "gather_probe.cu", "backward.cu", "noalloc.cu", "selftest.cu"]
+HEADERS = ["common.cuh", "ptx_sm100.cuh", "gemm_epilogue.cuh", os.path.join("..", "..", "include", "fmoe.h")]
 
 
 def _sources():

@@ -113,13 +113,15 @@ int mlp_up(const void* x, const void* gw, const void* uw, void* h, int dtype, in
   return launch_simt_gemm(x, H, gw, uw, nullptr, h, I, dtype, 1, T, I, H, stream);
 }
 
+// residual (nullable): [T, H] in the module dtype, added with the float32 addend before the single rounding
 int mlp_down(const void* h, const void* dw, const float* addend, void* out, int dtype, int64_t T, int H, int I,
-             int32_t* status, cudaStream_t stream) {
+             int32_t* status, cudaStream_t stream, const void* residual = nullptr) {
   const bool tc = is16(dtype) && (H % 8 == 0) && (I % 8 == 0) && aligned16(dw) && aligned16(out) &&
-                  (addend == nullptr || aligned16(addend));
-  if (tc && gemm_pair_supported(T, H, I)) return launch_gemm_add_pair(h, dw, addend, out, dtype, T, H, I, status, stream);
-  if (tc) return launch_gemm_add(h, dw, addend, out, dtype, T, H, I, status, stream);
-  return launch_simt_gemm(h, I, dw, nullptr, addend, out, H, dtype, 0, T, H, I, stream);
+                  (addend == nullptr || aligned16(addend)) && (residual == nullptr || aligned16(residual));
+  if (tc && gemm_pair_supported(T, H, I))
+    return launch_gemm_add_pair(h, dw, addend, out, dtype, T, H, I, status, stream, residual);
+  if (tc) return launch_gemm_add(h, dw, addend, out, dtype, T, H, I, status, stream, residual);
+  return launch_simt_gemm(h, I, dw, nullptr, addend, out, H, dtype, 0, T, H, I, stream, residual);
 }
 
 struct LayerWs {
@@ -201,11 +203,12 @@ int fmoe_bn_batch_sums(const void* x, int dtype, int64_t num_tokens, int hidden,
 int fmoe_expert_forward_sharded(const void* x, const void* const* down_shards, const void* const* up_shards,
                                 int num_shards, const int64_t* indices, const void* gates, void* out, int dtype,
                                 int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k,
-                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream) {
+                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream,
+                                const void* hot_down, const void* hot_up, int64_t num_hot) {
   if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
   return launch_expert_forward_peer(x, down_shards, up_shards, num_shards, indices, gates, out, dtype, out_dtype,
                                     num_tokens, hidden, num_experts, top_k, workspace, workspace_bytes, status,
-                                    static_cast<cudaStream_t>(stream));
+                                    static_cast<cudaStream_t>(stream), hot_down, hot_up, num_hot);
 }
 
 int fmoe_peer_forward(const void* x, const void* down, const void* up, const void* routing_weights,
@@ -378,6 +381,14 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   // stream it is forked AFTER the router GEMM (both want a whole SM's shared memory) so that the
   // tensor-core GEMM overlaps the latency-bound top-k and expert gathers that follow.
   ForkJoin* fj = nullptr;
+  // after the fork every early return first joins the side stream back into the caller's, so that a failed call
+  // never leaves a dangling branch (which would also invalidate a stream capture in progress)
+  auto fail = [&](int code) -> int {
+    if (fj != nullptr) {
+      if (cudaEventRecord(fj->join, s2) == cudaSuccess) (void)cudaStreamWaitEvent(s, fj->join, 0);
+    }
+    return code;
+  };
   if (s2 != nullptr && s2 != s) {
     fj = fork_join_events();
     if (fj == nullptr) return -static_cast<int>(cudaErrorUnknown);
@@ -385,7 +396,7 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
     FMOE_CUDA_TRY(cudaStreamWaitEvent(s2, fj->fork, 0));
     FMOE_MARK(FMOE_STAGE_MLP_UP, 0, s2);
     rc = mlp_up(a->x, a->gate_proj, a->up_proj, w.h, dtype, T, H, I, a->status, s2);
-    if (rc != FMOE_OK) return rc;
+    if (rc != FMOE_OK) return fail(rc);
     FMOE_MARK(FMOE_STAGE_MLP_UP, 1, s2);
     FMOE_CUDA_TRY(cudaEventRecord(fj->join, s2));
   }
@@ -399,11 +410,11 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   if (rc == FMOE_ERR_UNSUPPORTED) {
     if (topk_from_logits) {  // shapes the register kernel does not cover: explicit log-softmax pass
       rc = launch_log_softmax_halves(a->router_logits, w.logp, dtype, T, nk, s);
-      if (rc != FMOE_OK) return rc;
+      if (rc != FMOE_OK) return fail(rc);
     }
     rc = launch_router_topk(w.logp, dtype, T, nk, k, w.scores, indices, gates, a->norm_topk_prob ? 1 : 0, s);
   }
-  if (rc != FMOE_OK) return rc;
+  if (rc != FMOE_OK) return fail(rc);
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 1, s);
   FMOE_MARK(FMOE_STAGE_EXPERT_SCORES, 0, s);
 
@@ -420,21 +431,22 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   }
   rc = launch_expert_forward(a->x, a->down_embed, a->up_embed, indices, gates, w.acc, dtype, FMOE_DTYPE_F32, T, H, N, k,
                              w.expert, w.expert_bytes, a->status, s, between);
-  if (rc != FMOE_OK) return rc;
+  if (rc != FMOE_OK) return fail(rc);
   FMOE_MARK(FMOE_STAGE_EXPERT_ACCUM, 1, s);
 
   if (fj != nullptr) {
     FMOE_CUDA_TRY(cudaStreamWaitEvent(s, fj->join, 0));
+    fj = nullptr;  // joined
   } else {
     FMOE_MARK(FMOE_STAGE_MLP_UP, 0, s);
     rc = mlp_up(a->x, a->gate_proj, a->up_proj, w.h, dtype, T, H, I, a->status, s);
-    if (rc != FMOE_OK) return rc;
+    if (rc != FMOE_OK) return fail(rc);
     FMOE_MARK(FMOE_STAGE_MLP_UP, 1, s);
   }
   // y = h Wd^T + experts, one rounding
   FMOE_MARK(FMOE_STAGE_MLP_DOWN, 0, s);
-  rc = mlp_down(w.h, a->down_proj, static_cast<const float*>(w.acc), a->y, dtype, T, H, I, a->status, s);
-  if (rc != FMOE_OK) return rc;
+  rc = mlp_down(w.h, a->down_proj, static_cast<const float*>(w.acc), a->y, dtype, T, H, I, a->status, s, a->residual);
+  if (rc != FMOE_OK) return fail(rc);
   FMOE_MARK(FMOE_STAGE_MLP_DOWN, 1, s);
 #undef FMOE_MARK
   return FMOE_OK;

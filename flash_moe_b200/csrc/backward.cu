@@ -109,6 +109,7 @@ int launch_router_topk_backward(const void* dscores, const int64_t* indices, int
 
 int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* da, void* db, void* h, int dtype,
                            int64_t n, cudaStream_t stream) {
+  if (dtype != FMOE_DTYPE_F32 && dtype != FMOE_DTYPE_BF16 && dtype != FMOE_DTYPE_F16) return FMOE_ERR_BAD_ARG;
   if (n < 0) return FMOE_ERR_BAD_ARG;
   if (n == 0) return FMOE_OK;
   if (dh == nullptr || a == nullptr || b == nullptr || da == nullptr || db == nullptr) return FMOE_ERR_BAD_ARG;

@@ -129,9 +129,11 @@ int launch_expert_fused(const void* x, const void* down, const void* up, const i
                         float* raw_scores, int32_t* status, cudaStream_t stream);
 // the same sum with both tables sharded by e % world over the GPUs of a node; *_shards are DEVICE arrays of `world`
 // row-0 pointers (peer pointers for the other GPUs); 16-bit dtypes only
+// hot_down / hot_up (nullable): hot_rows rows replicated on every GPU, addressed by the ids N .. N + hot_rows - 1
 int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
                                const int64_t* indices, const void* gates, void* out, int dtype, int out_dtype, int64_t T,
-                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream);
+                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                               const void* hot_down = nullptr, const void* hot_up = nullptr, int64_t hot_rows = 0);
 // out[t] = sum_j weights[t,j] * values[indices[t,j]] (the PKM comparison op)
 int launch_weighted_rows(const void* values, const void* weights, const int64_t* indices, void* out, int dtype,
                          int64_t T, int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status,
@@ -142,8 +144,9 @@ int launch_weighted_rows(const void* values, const void* weights, const int64_t*
 // C[M,N] = A[M,K] * B[N,K]^T on tcgen05 with a fused epilogue (gemm_sm100.cu); bf16/fp16 only.
 int launch_gemm_swiglu(const void* x, const void* gate_w, const void* up_w, void* h, int dtype, int64_t M, int I, int K,
                        int32_t* status, cudaStream_t stream);
+// residual (nullable): [M, N] in the module dtype, added to the float32 sum before the single rounding
 int launch_gemm_add(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N, int K,
-                    int32_t* status, cudaStream_t stream);
+                    int32_t* status, cudaStream_t stream, const void* residual = nullptr);
 // router: per half h: logits[:, h*nk:(h+1)*nk] = A[:, h*a_half_koff : +K] * W[h*nk:(h+1)*nk, :K]^T, then log-softmax
 int launch_gemm_router(const void* xn, int64_t a_cols, int a_half_koff, const void* w, void* logits, void* log_probs,
                        int dtype, int64_t M, int nk, int K, int32_t* status, cudaStream_t stream);
@@ -159,11 +162,12 @@ int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w,
                             int K, int32_t* status, cudaStream_t stream, void* pre_gate = nullptr,
                             void* pre_up = nullptr);
 int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N,
-                         int K, int32_t* status, cudaStream_t stream);
+                         int K, int32_t* status, cudaStream_t stream, const void* residual = nullptr);
 
 // fp32-FMA GEMM on CUDA cores (simt_gemm.cu): float32 modules and shapes TMA cannot address.
 int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1, const float* addend, void* out,
-                     int64_t ldo, int dtype, int swiglu, int64_t M, int N, int K, cudaStream_t stream);
+                     int64_t ldo, int dtype, int swiglu, int64_t M, int N, int K, cudaStream_t stream,
+                     const void* residual = nullptr);
 
 // elementwise.cu
 int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, int64_t T, int nk, cudaStream_t stream);

@@ -252,9 +252,13 @@ template <> struct Mma16816<__half> {
 
 // Row e of a table that is either one array or, PEER, sharded over the GPUs of a node by e % world (shard r holds
 // expert e at row e / world; shards[r] may point into a peer GPU's memory, read with plain loads over NVLink).
+// In the sharded form ids at or above `sharded` address a small table replicated on every GPU (the hottest
+// experts, copied once): row e - sharded of `table`, which is local memory.
 template <typename T, bool PEER>
-__device__ __forceinline__ const T* table_row(const T* table, const T* const* shards, int world, int64_t e, int H) {
+__device__ __forceinline__ const T* table_row(const T* table, const T* const* shards, int world, int64_t e, int H,
+                                              int64_t sharded = 0) {
   if constexpr (PEER) {
+    if (e >= sharded) return table + (e - sharded) * H;
     const int64_t local = e / world;
     return shards[e - local * world] + local * H;
   } else {
@@ -274,7 +278,8 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
                                                                int64_t ntok, int H, int64_t N, int k, int xs_stride,
                                                                int32_t* status, int act,
                                                                const T* const* __restrict__ shards = nullptr,
-                                                               int world = 1, float* __restrict__ raw_out = nullptr) {
+                                                               int world = 1, float* __restrict__ raw_out = nullptr,
+                                                               int64_t sharded = 0) {
   extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -296,8 +301,8 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
     const bool oka = (ja < k) && ea >= 0 && ea < N;
     const bool okb = (jb < k) && eb >= 0 && eb < N;
     if ((ja < k && !oka && ea != -1) || (jb < k && !okb && eb != -1)) bad = true;  // -1: empty slot, no flag
-    const T* ra = table_row<T, PEER>(down, shards, world, oka ? ea : 0, H) + 8 * tq;
-    const T* rb = table_row<T, PEER>(down, shards, world, okb ? eb : 0, H) + 8 * tq;
+    const T* ra = table_row<T, PEER>(down, shards, world, oka ? ea : 0, H, sharded) + 8 * tq;
+    const T* rb = table_row<T, PEER>(down, shards, world, okb ? eb : 0, H, sharded) + 8 * tq;
     if (t != t_in_smem) {  // warp-uniform
       __syncwarp();
       const T* xr = x + t * H;
@@ -380,7 +385,7 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
                                                           const float* __restrict__ gs, OutT* __restrict__ out,
                                                           int64_t ntok, int H, int64_t N, int k, int colblocks,
                                                           const T* const* __restrict__ shards = nullptr,
-                                                          int world = 1) {
+                                                          int world = 1, int64_t sharded = 0) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int SLOTS = NCH >= 4 ? 4 : 8;
   const int lane = threadIdx.x & 31;
@@ -419,7 +424,7 @@ __global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__
           const int e = __shfl_sync(kFull, e_l, s + u);
           const float w = __shfl_sync(kFull, w_l, s + u);
           ww[u] = pack_f32x2(w, w);
-          const T* row = table_row<T, PEER>(up, shards, world, e, H) + col0 + lane * VEC;
+          const T* row = table_row<T, PEER>(up, shards, world, e, H, sharded) + col0 + lane * VEC;
 #pragma unroll
           for (int c = 0; c < NCH; ++c) q[u][c] = in[c] ? ldg16(row + c * 32 * VEC) : make_uint4(0, 0, 0, 0);
         }
@@ -891,10 +896,12 @@ __global__ void __launch_bounds__(256) expert_bwd_finish_kernel(const int* __res
 
 // Tables sharded over the GPUs of one node, rows of the other GPUs read through peer pointers: the two gather
 // kernels of the per-token schedule with the row address computed from (e % world, e / world).
+// hot_down / hot_up (nullable, hot_rows rows): tables replicated on every GPU, addressed by the ids N .. N + hot_rows - 1
 template <typename T>
 int run_typed_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
                    const int64_t* idx, const void* gates, void* out, int out_f32, int64_t T_, int H, int64_t N, int k,
-                   const ExpertWs& w, int32_t* status, cudaStream_t stream) {
+                   const ExpertWs& w, int32_t* status, cudaStream_t stream, const void* hot_down, const void* hot_up,
+                   int64_t hot_rows) {
   if constexpr (sizeof(T) != 2) {
     return FMOE_ERR_UNSUPPORTED;
   } else {
@@ -908,9 +915,9 @@ int run_typed_peer(const void* x, const void* const* down_shards, const void* co
       const int smem = 4 * xs_stride * 16;
       auto kern = expert_scores_mma_kernel<T, 4, true, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), nullptr, idx, static_cast<const T*>(gates), w.gs, T_, H,
-                                        N, k, xs_stride, status, kActSilu,
-                                        reinterpret_cast<const T* const*>(down_shards), world, nullptr);
+      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), static_cast<const T*>(hot_down), idx,
+                                        static_cast<const T*>(gates), w.gs, T_, H, N + hot_rows, k, xs_stride, status,
+                                        kActSilu, reinterpret_cast<const T* const*>(down_shards), world, nullptr, N);
       FMOE_LAUNCH_CHECK();
     }
     const int need = (H + 32 * VEC - 1) / (32 * VEC);
@@ -920,9 +927,10 @@ int run_typed_peer(const void* x, const void* const* down_shards, const void* co
     const int64_t cap = static_cast<int64_t>(sms) * 16;
     const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
     const T* const* us = reinterpret_cast<const T* const*>(up_shards);
-#define FMOE_PEER_ACCUM(OUT_, NCH_)                                                                                \
-  expert_accum_kernel<T, OUT_, NCH_, true><<<grid, 128, 0, stream>>>(nullptr, idx, w.gs, static_cast<OUT_*>(out), T_, \
-                                                                     H, N, k, colblocks, us, world)
+#define FMOE_PEER_ACCUM(OUT_, NCH_)                                                                            \
+  expert_accum_kernel<T, OUT_, NCH_, true><<<grid, 128, 0, stream>>>(static_cast<const T*>(hot_up), idx, w.gs,    \
+                                                                     static_cast<OUT_*>(out), T_, H, N + hot_rows, k, \
+                                                                     colblocks, us, world, N)
     if (out_f32) {
       if (nch == 1) FMOE_PEER_ACCUM(float, 1);
       else FMOE_PEER_ACCUM(float, 2);
@@ -1180,14 +1188,17 @@ int launch_weighted_rows(const void* values, const void* weights, const int64_t*
 
 int launch_expert_forward_peer(const void* x, const void* const* down_shards, const void* const* up_shards, int world,
                                const int64_t* indices, const void* gates, void* out, int dtype, int out_dtype, int64_t T,
-                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
-  if (T < 0 || H <= 0 || N <= 0 || k < 0 || world < 1) return FMOE_ERR_BAD_ARG;
+                               int H, int64_t N, int k, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                               const void* hot_down, const void* hot_up, int64_t hot_rows) {
+  if (T < 0 || H <= 0 || N <= 0 || k < 0 || world < 1 || hot_rows < 0) return FMOE_ERR_BAD_ARG;
+  if (hot_rows > 0 && (hot_down == nullptr || hot_up == nullptr || !aligned16(hot_down) || !aligned16(hot_up)))
+    return FMOE_ERR_BAD_ARG;
   if (out_dtype != dtype && out_dtype != FMOE_DTYPE_F32) return FMOE_ERR_BAD_ARG;
   if (dtype == FMOE_DTYPE_F32) return FMOE_ERR_UNSUPPORTED;
   if (T == 0) return FMOE_OK;
   if (x == nullptr || down_shards == nullptr || up_shards == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
   if (k > 0 && (indices == nullptr || gates == nullptr)) return FMOE_ERR_BAD_ARG;
-  if (N > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
+  if (N + hot_rows > 0x7FFFFFFFll || T * static_cast<int64_t>(k) > 0x7FFFFFFFll) return FMOE_ERR_UNSUPPORTED;
   if (H % 8 != 0 || !aligned16(x) || !aligned16(out)) return FMOE_ERR_ALIGNMENT;
   if (k == 0) {
     FMOE_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(T) * H * dtype_size(out_dtype), stream));
@@ -1198,10 +1209,10 @@ int launch_expert_forward_peer(const void* x, const void* const* down_shards, co
   const int out_f32 = (out_dtype == FMOE_DTYPE_F32) ? 1 : 0;
   if (dtype == FMOE_DTYPE_BF16)
     return run_typed_peer<__nv_bfloat16>(x, down_shards, up_shards, world, indices, gates, out, out_f32, T, H, N, k, w,
-                                         status, stream);
+                                         status, stream, hot_down, hot_up, hot_rows);
   if (dtype == FMOE_DTYPE_F16)
     return run_typed_peer<__half>(x, down_shards, up_shards, world, indices, gates, out, out_f32, T, H, N, k, w, status,
-                                  stream);
+                                  stream, hot_down, hot_up, hot_rows);
   return FMOE_ERR_BAD_ARG;
 }
 

@@ -12,10 +12,7 @@
 //   warps 2..5         epilogue: tcgen05.ld the accumulator (one row per thread), round, store.
 // Columns of x beyond K arrive as zeros from TMA and are normalised with mean 0 / scale 0, so they stay zero.
 // Every wait is bounded; a wait that runs out raises FMOE_STATUS_WAIT_TIMEOUT and the CTA drains and leaves.
-#include <cuda.h>
-
-#include "common.cuh"
-#include "ptx_sm100.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace fmoe {
 namespace {
@@ -28,9 +25,7 @@ constexpr int kThreads = (2 + kXformWarps) * 32;
 constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
 constexpr unsigned kFull = 0xFFFFFFFFu;
 
-template <typename T> struct UmmaFmt;
-template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
-template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0; };
+using epi::UmmaFmt;
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -118,7 +113,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!ok) {  // let the copies already issued land before the CTA goes away (bounded)
         const int first = kb > kStages ? kb - kStages : 0;
         for (int j = first; j < kb; ++j)
-          ptx::mbar_wait_bounded(full_bar(j % kStages), (j / kStages) & 1u, abort_flag, 2000000ull);
+          ptx::mbar_wait_drain(full_bar(j % kStages), (j / kStages) & 1u);
       }
     }
   } else if (warp == 1) {
@@ -184,25 +179,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
         const int64_t row = static_cast<int64_t>(m_tile) * BLOCK_M + q4 * 32 + lane;
-        T* orow = out + row * N;
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
-          uint32_t a[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, a);
-          ptx::tmem_ld_wait();
-          const int col0 = n_tile * BLOCK_N + c * 32;
-          if (row < M) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col0 + v * 8 < N) {
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
-                *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
-              }
-            }
-          }
-        }
+        epi::store_add_row<T, BLOCK_N>(taddr, out + row * N, nullptr, nullptr, n_tile * BLOCK_N, N, row < M);
       }
     }
   }
@@ -218,34 +195,8 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag != 0 && status != nullptr) atomicOr(status, FMOE_STATUS_WAIT_TIMEOUT);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encoder() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
 int make_map(CUtensorMap* m, const void* basep, int dtype, uint64_t cols, uint64_t rows, uint32_t box_rows) {
-  EncodeTiledFn fn = encoder();
-  if (fn == nullptr) return -static_cast<int>(cudaErrorNotSupported);
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {BLOCK_K, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = dtype == FMOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = fn(m, dt, 2, const_cast<void*>(basep), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FMOE_OK : FMOE_ERR_BAD_ARG;
+  return epi::make_tensor_map(m, basep, dtype, cols, rows, cols, box_rows);
 }
 
 template <int BLOCK_N, typename T>

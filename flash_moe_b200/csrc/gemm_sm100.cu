@@ -13,12 +13,10 @@
 //   ADD     out = acc (+ fp32 addend), one rounding                                        (bf16)
 //   ROUTER  one router half per N tile: logits rounded to the module dtype, then the per-half
 //           log-softmax of those rounded logits (flash_moe/modules/flash_moe.py:65-72)
-// Every wait is bounded; on a timeout the CTA flags FMOE_STATUS_WAIT_TIMEOUT, drains and exits.
+// Every mbarrier wait is bounded; on a timeout the CTA flags FMOE_STATUS_WAIT_TIMEOUT, drains and exits.
+// (tcgen05.alloc itself blocks until tensor memory is free, i.e. until an earlier CTA on the SM has released it.)
 // No cluster launch and no multicast: each CTA loads its own operands.
-#include <cuda.h>
-
-#include "common.cuh"
-#include "ptx_sm100.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace fmoe {
 namespace {
@@ -36,6 +34,7 @@ struct EpiParams {
   void* out;            // ADD: out[M, ldo]; SWIGLU: h[M, ldo]; ROUTER: logits[M, ldo]
   void* out2;           // ROUTER: log_probs[2, M, n_valid]
   const float* addend;  // ADD: optional fp32 [M, ldo]
+  const void* residual; // ADD: optional [M, ldo] in the module dtype, added before the single rounding
   int64_t ldo;
   int n_valid;      // ADD: N; SWIGLU: I; ROUTER: num_keys
   int a_half_koff;  // ROUTER: K offset of half 1 inside a row of A
@@ -52,9 +51,7 @@ template <int BLOCK_N> struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
 };
 
-template <typename T> struct UmmaFmt;
-template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
-template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0; };
+using epi::UmmaFmt;
 
 template <int BLOCK_N, int EPI, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -134,7 +131,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // let the copies already issued land before the CTA goes away (bounded)
         const uint32_t first = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
         for (uint32_t j = first; j < it; ++j)
-          ptx::mbar_wait_bounded(full_bar(j % STAGES), (j / STAGES) & 1u, abort_flag, 2000000ull);
+          ptx::mbar_wait_drain(full_bar(j % STAGES), (j / STAGES) & 1u);
       }
     }
   } else if (warp == 1) {
@@ -188,63 +185,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
       if constexpr (EPI == EPI_SWIGLU) {
         T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 64; ++c) {
-          uint32_t g[32], u[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, g);
-          ptx::tmem_ld_32x32(taddr + BLOCK_N / 2 + c * 32, u);
-          ptx::tmem_ld_wait();
-          const int col0 = n_tile * (BLOCK_N / 2) + c * 32;
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                f[i] = silu_f32(__uint_as_float(g[v * 8 + i])) * __uint_as_float(u[v * 8 + i]);
-              if (col0 + v * 8 < ep.n_valid) *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
-            }
-          }
-        }
+        epi::store_swiglu_row<T, BLOCK_N>(taddr, orow, nullptr, nullptr, n_tile * (BLOCK_N / 2), ep.n_valid, row_ok);
       } else if constexpr (EPI == EPI_ADD) {
         T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
         const float* arow = (ep.addend != nullptr && row_ok) ? ep.addend + row * ep.ldo : nullptr;
-        constexpr int NCHUNK = BLOCK_N / 32;
-        // the fp32 addend of the next 32 columns is fetched while the current chunk is processed
-        float4 nxt[8];
-        auto fetch = [&](int c) {
-          const int col0 = n_tile * BLOCK_N + c * 32;
-#pragma unroll
-          for (int v = 0; v < 8; ++v)
-            nxt[v] = (arow != nullptr && col0 + v * 4 < ep.n_valid)
-                         ? __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 4))
-                         : make_float4(0.f, 0.f, 0.f, 0.f);
-        };
-        fetch(0);
-#pragma unroll 1
-        for (int c = 0; c < NCHUNK; ++c) {
-          float4 cur[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
-          if (c + 1 < NCHUNK) fetch(c + 1);
-          uint32_t a[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, a);
-          ptx::tmem_ld_wait();
-          const int col0 = n_tile * BLOCK_N + c * 32;
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col0 + v * 8 < ep.n_valid) {
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
-                f[0] += cur[2 * v].x; f[1] += cur[2 * v].y; f[2] += cur[2 * v].z; f[3] += cur[2 * v].w;
-                f[4] += cur[2 * v + 1].x; f[5] += cur[2 * v + 1].y; f[6] += cur[2 * v + 1].z; f[7] += cur[2 * v + 1].w;
-                *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
-              }
-            }
-          }
-        }
+        const T* rrow = (ep.residual != nullptr && row_ok) ? static_cast<const T*>(ep.residual) + row * ep.ldo : nullptr;
+        epi::store_add_row<T, BLOCK_N>(taddr, orow, arow, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok);
       } else {  // EPI_ROUTER: n_tile is the router half
         const int nk = ep.n_valid;
         const bool vec_ok = (nk % 8) == 0;
@@ -327,36 +273,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
 // 2-D K-major operand: `rows` rows of `cols` elements, row pitch `pitch` elements; box = 64 x box_rows.
 int make_tmap(CUtensorMap* m, const void* basep, int dtype, uint64_t cols, uint64_t rows, uint64_t pitch,
               uint32_t box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) return -static_cast<int>(cudaErrorNotSupported);
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {pitch * 2};
-  const cuuint32_t box[2] = {BLOCK_K, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = dtype == FMOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = fn(m, dt, 2, const_cast<void*>(basep), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FMOE_OK : FMOE_ERR_BAD_ARG;
+  return epi::make_tensor_map(m, basep, dtype, cols, rows, pitch, box_rows);
 }
 
 template <int BLOCK_N, int EPI, typename T>
@@ -397,7 +317,7 @@ int launch_gemm_swiglu(const void* x, const void* gate_w, const void* up_w, void
   if ((rc = make_tmap(&tA, x, dtype, K, M, K, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_tmap(&tG, gate_w, dtype, K, I, K, 128)) != FMOE_OK) return rc;
   if ((rc = make_tmap(&tU, up_w, dtype, K, I, K, 128)) != FMOE_OK) return rc;
-  EpiParams ep{h, nullptr, nullptr, I, I, 0};
+  EpiParams ep{h, nullptr, nullptr, nullptr, I, I, 0};
   const int n_tiles = (I + 127) / 128;
   if (dtype == FMOE_DTYPE_BF16)
     return launch<256, EPI_SWIGLU, __nv_bfloat16>(tA, tG, tU, ep, M, n_tiles, K, status, stream);
@@ -405,14 +325,15 @@ int launch_gemm_swiglu(const void* x, const void* gate_w, const void* up_w, void
 }
 
 int launch_gemm_add(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N, int K,
-                    int32_t* status, cudaStream_t stream) {
+                    int32_t* status, cudaStream_t stream, const void* residual) {
   int rc = check_gemm_args(a, b, out, dtype, M, K);
   if (rc != FMOE_OK) return rc;
   if (N <= 0) return FMOE_ERR_BAD_ARG;
-  if (N % 8 != 0 || (addend != nullptr && !aligned16(addend))) return FMOE_ERR_ALIGNMENT;
+  if (N % 8 != 0 || (addend != nullptr && !aligned16(addend)) || (residual != nullptr && !aligned16(residual)))
+    return FMOE_ERR_ALIGNMENT;
   CUtensorMap tA, tB;
   if ((rc = make_tmap(&tA, a, dtype, K, M, K, BLOCK_M)) != FMOE_OK) return rc;
-  EpiParams ep{out, nullptr, addend, N, N, 0};
+  EpiParams ep{out, nullptr, addend, residual, N, N, 0};
   const int64_t m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
   const bool wide = N > 128 && m_tiles * ((N + 255) / 256) * 2 > device_sm_count();
   if (wide) {
@@ -442,7 +363,7 @@ int launch_gemm_router(const void* xn, int64_t a_cols, int a_half_koff, const vo
   CUtensorMap tA, tB;
   if ((rc = make_tmap(&tA, xn, dtype, a_cols, M, a_cols, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_tmap(&tB, w, dtype, K, 2 * static_cast<uint64_t>(nk), K, bn)) != FMOE_OK) return rc;
-  EpiParams ep{logits, log_probs, nullptr, 2 * static_cast<int64_t>(nk), nk, a_half_koff};
+  EpiParams ep{logits, log_probs, nullptr, nullptr, 2 * static_cast<int64_t>(nk), nk, a_half_koff};
 #define FMOE_ROUTER_CASE(BN)                                                                               \
   case BN:                                                                                                 \
     if (dtype == FMOE_DTYPE_BF16)                                                                          \

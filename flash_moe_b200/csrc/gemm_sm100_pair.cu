@@ -15,11 +15,9 @@
 //   * each CTA's epilogue warps drain their own 128 accumulator rows and arrive on the leader's
 //     `tmem_empty` barrier (8 arrivals);
 //   * cluster barriers bracket set-up and tear-down so no CTA touches a peer that is not there.
-// No multicast loads anywhere; every wait is bounded like in the single-CTA kernel.
-#include <cuda.h>
-
-#include "common.cuh"
-#include "ptx_sm100.cuh"
+// No multicast loads anywhere; every mbarrier wait is bounded like in the single-CTA kernel (tcgen05.alloc blocks
+// until tensor memory is free on the SM, which an earlier CTA of this library always releases).
+#include "gemm_epilogue.cuh"
 
 namespace fmoe {
 namespace {
@@ -42,15 +40,14 @@ enum { PAIR_EPI_ADD = 0, PAIR_EPI_SWIGLU = 1 };
 struct PairEpi {
   void* out;
   const float* addend;
+  const void* residual;  // ADD only, nullable: [M, ldo] in the module dtype, added before the single rounding
   int64_t ldo;
   int n_valid;
   void* pre_gate;  // SWIGLU only, nullable: x Wg^T and x Wu^T rounded to T, kept for the backward pass
   void* pre_up;
 };
 
-template <typename T> struct UmmaFmt;
-template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
-template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0; };
+using epi::UmmaFmt;
 
 template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -128,6 +125,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
         }
       }
+      if (!ok && rank == 0) {
+        // gave up: the leader's `full` barriers count the bytes of BOTH CTAs, so once the leader has seen the
+        // stages still in flight complete, neither CTA has a copy on its way; the peer stays until the cluster
+        // barrier of the teardown, which the leader reaches only after this loop
+        const uint32_t first = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
+        for (uint32_t j = first; j < it; ++j) ptx::mbar_wait_drain(full_bar(j % STAGES), (j / STAGES) & 1u);
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -176,78 +180,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int64_t row = static_cast<int64_t>(m_tile) * (2 * BLOCK_M) + rank * BLOCK_M + row_in_tile;
       const bool row_ok = row < M;
 
+      T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
       if constexpr (EPI == PAIR_EPI_SWIGLU) {
-        T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
         T* grow = ep.pre_gate != nullptr ? static_cast<T*>(ep.pre_gate) + row * ep.ldo : nullptr;
         T* urow = ep.pre_up != nullptr ? static_cast<T*>(ep.pre_up) + row * ep.ldo : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 64; ++c) {
-          uint32_t g[32], u[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, g);
-          ptx::tmem_ld_32x32(taddr + BLOCK_N / 2 + c * 32, u);
-          ptx::tmem_ld_wait();
-          const int col0 = n_tile * (BLOCK_N / 2) + c * 32;
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                f[i] = silu_f32(__uint_as_float(g[v * 8 + i])) * __uint_as_float(u[v * 8 + i]);
-              if (col0 + v * 8 < ep.n_valid) {
-                *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
-                if (grow != nullptr) {
-                  float fg[8], fu[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    fg[i] = __uint_as_float(g[v * 8 + i]);
-                    fu[i] = __uint_as_float(u[v * 8 + i]);
-                  }
-                  *reinterpret_cast<uint4*>(grow + col0 + v * 8) = pack16<T>(fg);
-                  *reinterpret_cast<uint4*>(urow + col0 + v * 8) = pack16<T>(fu);
-                }
-              }
-            }
-          }
-        }
+        epi::store_swiglu_row<T, BLOCK_N>(taddr, orow, grow, urow, n_tile * (BLOCK_N / 2), ep.n_valid, row_ok);
       } else {
-        T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
         const float* arow = (ep.addend != nullptr && row_ok) ? ep.addend + row * ep.ldo : nullptr;
-        constexpr int NCHUNK = BLOCK_N / 32;
-        float4 nxt[8];
-        auto fetch = [&](int c) {
-          const int col0 = n_tile * BLOCK_N + c * 32;
-#pragma unroll
-          for (int v = 0; v < 8; ++v)
-            nxt[v] = (arow != nullptr && col0 + v * 4 < ep.n_valid)
-                         ? __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 4))
-                         : make_float4(0.f, 0.f, 0.f, 0.f);
-        };
-        fetch(0);
-#pragma unroll 1
-        for (int c = 0; c < NCHUNK; ++c) {
-          float4 cur[8];
-#pragma unroll
-          for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
-          if (c + 1 < NCHUNK) fetch(c + 1);
-          uint32_t a[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, a);
-          ptx::tmem_ld_wait();
-          const int col0 = n_tile * BLOCK_N + c * 32;
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col0 + v * 8 < ep.n_valid) {
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
-                f[0] += cur[2 * v].x; f[1] += cur[2 * v].y; f[2] += cur[2 * v].z; f[3] += cur[2 * v].w;
-                f[4] += cur[2 * v + 1].x; f[5] += cur[2 * v + 1].y; f[6] += cur[2 * v + 1].z; f[7] += cur[2 * v + 1].w;
-                *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
-              }
-            }
-          }
-        }
+        const T* rrow = (ep.residual != nullptr && row_ok) ? static_cast<const T*>(ep.residual) + row * ep.ldo : nullptr;
+        epi::store_add_row<T, BLOCK_N>(taddr, orow, arow, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok);
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -266,34 +207,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0 && *abort_flag != 0 && status != nullptr) atomicOr(status, FMOE_STATUS_WAIT_TIMEOUT);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
 int make_map(CUtensorMap* m, const void* basep, int dtype, uint64_t cols, uint64_t rows, uint32_t box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return -static_cast<int>(cudaErrorNotSupported);
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {BLOCK_K, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = dtype == FMOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = fn(m, dt, 2, const_cast<void*>(basep), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FMOE_OK : FMOE_ERR_BAD_ARG;
+  return epi::make_tensor_map(m, basep, dtype, cols, rows, cols, box_rows);
 }
 
 template <int EPI, typename T>
@@ -337,7 +252,7 @@ int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w,
   if ((rc = make_map(&tG, gate_w, dtype, K, I, BLOCK_N / 2)) != FMOE_OK) return rc;
   if ((rc = make_map(&tU, up_w, dtype, K, I, BLOCK_N / 2)) != FMOE_OK) return rc;
   if ((pre_gate == nullptr) != (pre_up == nullptr)) return FMOE_ERR_BAD_ARG;
-  PairEpi ep{h, nullptr, I, I, pre_gate, pre_up};
+  PairEpi ep{h, nullptr, nullptr, I, I, pre_gate, pre_up};
   const int n_tiles = (I + 127) / 128;
   if (dtype == FMOE_DTYPE_BF16)
     return launch_pair<PAIR_EPI_SWIGLU, __nv_bfloat16>(tA, tG, tU, ep, M, n_tiles, K, status, stream);
@@ -345,12 +260,12 @@ int launch_gemm_swiglu_pair(const void* x, const void* gate_w, const void* up_w,
 }
 
 int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void* out, int dtype, int64_t M, int N,
-                         int K, int32_t* status, cudaStream_t stream) {
+                         int K, int32_t* status, cudaStream_t stream, const void* residual) {
   CUtensorMap tA, tB;
   int rc;
   if ((rc = make_map(&tA, a, dtype, K, M, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_map(&tB, b, dtype, K, N, BLOCK_N / 2)) != FMOE_OK) return rc;
-  PairEpi ep{out, addend, N, N, nullptr, nullptr};
+  PairEpi ep{out, addend, residual, N, N, nullptr, nullptr};
   const int n_tiles = (N + 255) / 256;
   if (dtype == FMOE_DTYPE_BF16)
     return launch_pair<PAIR_EPI_ADD, __nv_bfloat16>(tA, tB, tB, ep, M, n_tiles, K, status, stream);

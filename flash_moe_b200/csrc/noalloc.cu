@@ -17,8 +17,11 @@
 //     call, nothing else is assumed about its contents;
 //   * two calls that overlap on the GPU (different streams, no ordering between them) race on
 //     the array - serialise them on one stream or with events;
-//   * the first call on each device resolves the array's device address
-//     (cudaGetSymbolAddress); make that first call outside any stream capture.
+//   * the first call on each device resolves the array's device address (cudaGetSymbolAddress) - with lazy module
+//     loading that can be when the driver loads this library's device code, the 8 MiB included; make that first call
+//     during warm-up, outside any stream capture.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -29,18 +32,19 @@ static __device__ __align__(256) unsigned char g_expert_scratch[kStaticScratchBy
 
 // In host code `g_expert_scratch` is only a handle for the runtime, not an address a kernel can
 // use; the device address is looked up once per device, with that device current.
+// Host threads may race to fill a slot: they all look up the same address, and the slot is atomic.
 int static_scratch(void** out) {
-  static void* cache[64] = {nullptr};
+  static std::atomic<void*> cache[64];
   int dev = 0;
   FMOE_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return FMOE_ERR_UNSUPPORTED;
-  if (cache[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = cache[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     FMOE_CUDA_TRY(cudaGetSymbolAddress(&p, g_expert_scratch));
     if (p == nullptr) return -static_cast<int>(cudaErrorInvalidSymbol);
-    cache[dev] = p;
+    cache[dev].store(p, std::memory_order_release);
   }
-  *out = cache[dev];
+  *out = p;
   return FMOE_OK;
 }
 

@@ -64,6 +64,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
+// Wait used on the give-up path only: lets copies that were already issued land before their destination (this
+// CTA's shared memory) goes away.  Ignores the abort flag (it is set by then) and has its own short limit.
+__device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity, uint64_t limit_ns = 20000000ull) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < (1u << 24); ++it) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) return;
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -12,7 +12,8 @@ constexpr int TM = 64, TN = 64, TK = 16;
 template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(256) simt_gemm_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ B0,
                                                        const T* __restrict__ B1, int64_t ldb,
-                                                       const float* __restrict__ addend, T* __restrict__ out,
+                                                       const float* __restrict__ addend,
+                                                       const T* __restrict__ residual, T* __restrict__ out,
                                                        int64_t ldo, int M, int N, int K) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Bs0[TK][TN + 4];
@@ -65,8 +66,9 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const T* __restrict__ A,
       float v = acc0[i][j];
       if (SWIGLU) {
         v = (v / (1.0f + expf(-v))) * acc1[i][j];
-      } else if (addend != nullptr) {
-        v += addend[static_cast<int64_t>(m) * ldo + n];
+      } else {
+        if (addend != nullptr) v += addend[static_cast<int64_t>(m) * ldo + n];
+        if (residual != nullptr) v += to_f32<T>(residual[static_cast<int64_t>(m) * ldo + n]);
       }
       out[static_cast<int64_t>(m) * ldo + n] = from_f32<T>(v);
     }
@@ -75,16 +77,16 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const T* __restrict__ A,
 
 template <typename T>
 int run(const void* a, int64_t lda, const void* b0, const void* b1, const float* addend, void* out, int64_t ldo,
-        int swiglu, int64_t M, int N, int K, cudaStream_t stream) {
+        int swiglu, int64_t M, int N, int K, cudaStream_t stream, const void* residual) {
   dim3 grid((N + TN - 1) / TN, static_cast<unsigned>((M + TM - 1) / TM));
   if (swiglu)
     simt_gemm_kernel<T, true><<<grid, 256, 0, stream>>>(static_cast<const T*>(a), lda, static_cast<const T*>(b0),
-                                                        static_cast<const T*>(b1), K, nullptr, static_cast<T*>(out),
-                                                        ldo, static_cast<int>(M), N, K);
+                                                        static_cast<const T*>(b1), K, nullptr, nullptr,
+                                                        static_cast<T*>(out), ldo, static_cast<int>(M), N, K);
   else
     simt_gemm_kernel<T, false><<<grid, 256, 0, stream>>>(static_cast<const T*>(a), lda, static_cast<const T*>(b0),
-                                                         nullptr, K, addend, static_cast<T*>(out), ldo,
-                                                         static_cast<int>(M), N, K);
+                                                         nullptr, K, addend, static_cast<const T*>(residual),
+                                                         static_cast<T*>(out), ldo, static_cast<int>(M), N, K);
   FMOE_LAUNCH_CHECK();
   return FMOE_OK;
 }
@@ -92,13 +94,14 @@ int run(const void* a, int64_t lda, const void* b0, const void* b1, const float*
 }  // namespace
 
 int launch_simt_gemm(const void* a, int64_t lda, const void* b0, const void* b1, const float* addend, void* out,
-                     int64_t ldo, int dtype, int swiglu, int64_t M, int N, int K, cudaStream_t stream) {
+                     int64_t ldo, int dtype, int swiglu, int64_t M, int N, int K, cudaStream_t stream,
+                     const void* residual) {
   if (a == nullptr || b0 == nullptr || out == nullptr || (swiglu && b1 == nullptr)) return FMOE_ERR_BAD_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7FFFFFFFll - TM || (M + TM - 1) / TM > 65535) return FMOE_ERR_UNSUPPORTED;
   switch (dtype) {
-    case FMOE_DTYPE_F32: return run<float>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream);
-    case FMOE_DTYPE_BF16: return run<__nv_bfloat16>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream);
-    case FMOE_DTYPE_F16: return run<__half>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream);
+    case FMOE_DTYPE_F32: return run<float>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream, residual);
+    case FMOE_DTYPE_BF16: return run<__nv_bfloat16>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream, residual);
+    case FMOE_DTYPE_F16: return run<__half>(a, lda, b0, b1, addend, out, ldo, swiglu, M, N, K, stream, residual);
     default: return FMOE_ERR_BAD_ARG;
   }
 }

@@ -116,16 +116,21 @@ class FlashMoE(nn.Module):
         return ws
 
     def kernels_per_forward(self) -> int:
-        """Kernels of this library launched by one forward (16-bit dtypes): batch-norm apply, router GEMM,
-        top-k (with the log-softmax inside for num_keys <= 1024), experts (2 kernels for 16-bit dtypes, which
-        are gathered per token; 5 with the expert-centric sort of float32), MLP up GEMM, MLP down GEMM."""
-        n = 1 + 1 + 1 + 1 + 1
-        if self.num_keys > 1024:
+        """Kernels of this library launched by one fused forward: router GEMM (16-bit modules: the batch-norm is applied
+        inside it; float32: a separate normalisation pass), top-k (with the log-softmax inside for num_keys <= 1024),
+        experts (16-bit tables: scores + accumulate, or one fused kernel once a table reaches 1 GiB; float32: histogram,
+        scan, scatter, scores, accumulate), MLP up GEMM, MLP down GEMM; training adds the batch statistics passes."""
+        sixteen = self.down_embed.weight.element_size() == 2
+        n = 1 + 1 + 1 + 1  # router GEMM, top-k, MLP up, MLP down
+        if not sixteen or self.hidden_size % 8 != 0 or self.hidden_size > 3072 or (2 * self.num_keys) % 8 != 0:
+            n += 1  # stand-alone normalisation pass
+        if self.num_keys > 1024 or not sixteen:
             n += 1  # separate log-softmax pass
-        if self.down_embed.weight.element_size() == 2:
-            n += 2  # scores (mma) + accumulate
+        if sixteen:
+            big = self.num_experts * self.hidden_size * 2 >= (1 << 30) and self.hidden_size <= 2048
+            n += 1 if big else 2
         else:
-            n += 5  # histogram, scan, scatter, scores, accumulate
+            n += 5
             if (self.num_experts + 2047) // 2048 > 16:
                 n += 1  # two-level scan
         if self.training:
@@ -159,6 +164,7 @@ class FlashMoE(nn.Module):
         return_routing: bool = False,
         stage_timer: Optional[StageTimer] = None,
         bn_sync_group=None,
+        residual: Optional[torch.Tensor] = None,
         **kwargs,
     ) -> Tuple[torch.Tensor, torch.Tensor]:
         """(y[B,S,H], router_logits[2, B*S, num_keys]) like the reference.
@@ -174,13 +180,18 @@ class FlashMoE(nn.Module):
 
         ``return_routing=True`` additionally keeps the selected expert ids and gates in
         ``self.last_indices`` / ``self.last_gates``.
+
+        ``residual`` (same shape and dtype as ``hidden_states``): the skip connection of the surrounding decoder
+        block.  The fused path adds it in the epilogue of the last GEMM, so ``residual + layer(x)`` is formed in
+        float32 and rounded once; the differentiable path adds it as a separate autograd node.
         """
         bsz, seq_len, _ = hidden_states.shape
         dev = _lib.require_cuda(hidden_states)
         if torch.is_grad_enabled() and (hidden_states.requires_grad or any(p.requires_grad for p in self.parameters())):
             if bn_sync_group is not None or stage_timer is not None:
                 raise _lib.FmoeError("bn_sync_group and stage_timer belong to the fused path: call under torch.no_grad()")
-            return self._forward_differentiable(hidden_states, return_routing)
+            y, router_logits = self._forward_differentiable(hidden_states, return_routing)
+            return (y if residual is None else residual + y), router_logits
         x = hidden_states.reshape(-1, self.hidden_size)
         if not x.is_contiguous():
             x = x.contiguous()
@@ -190,9 +201,24 @@ class FlashMoE(nn.Module):
             raise _lib.FmoeError(f"module is {w.dtype} on {w.device}, input is {dtype} on {dev}")
         T = x.shape[0]
         H, I, N, nk, k = self.hidden_size, self.intermediate_size, self.num_experts, self.num_keys, self.top_k
+        res = None
+        if residual is not None:
+            if residual.shape != hidden_states.shape or residual.dtype != dtype or residual.device != dev:
+                raise _lib.FmoeError("residual must match hidden_states in shape, dtype and device")
+            res = residual.reshape(-1, H)
+            if not res.is_contiguous():
+                res = res.contiguous()
         bn = self.router_norm
         training = bool(self.training) or bn.running_mean is None
-        momentum = 0.1 if bn.momentum is None else float(bn.momentum)
+        if training and T == 1:
+            # nn.BatchNorm1d refuses a one-row training batch (its variance is undefined); so does this layer
+            raise ValueError("Expected more than 1 value per channel when training, got input size " + str(list(x.shape)))
+        if bn.momentum is None:
+            # torch's cumulative moving average: the factor is 1 / (batches seen, this one included)
+            seen = int(bn.num_batches_tracked.item()) if bn.num_batches_tracked is not None else 0
+            momentum = 1.0 / float(seen + 1)
+        else:
+            momentum = float(bn.momentum)
 
         y = torch.empty((T, H), device=dev, dtype=dtype)
         logits = torch.empty((T, 2 * nk), device=dev, dtype=dtype)
@@ -250,6 +276,7 @@ class FlashMoE(nn.Module):
             a.bn_eps = float(bn.eps)
             a.bn_global_sums = _lib.ptr(bn_sums)
             a.bn_global_count = bn_count
+            a.residual = _lib.ptr(res)
             rc = L.fmoe_layer_forward(ctypes.byref(a))
         _lib.check(rc, "fmoe_layer_forward")
         # The side stream is joined back into the calling stream inside the library call, so the
@@ -263,26 +290,31 @@ class FlashMoE(nn.Module):
 
 
 class GraphedFlashMoE:
-    """One layer forward captured in a CUDA graph for a fixed input shape: the seven kernels replay
-    back to back without per-launch host work.  Write the input into ``static_input`` (or pass it to
-    ``__call__``, which copies it there), then read ``static_output`` / ``static_router_logits``; they
-    are overwritten by the next replay."""
+    """A forward captured in a CUDA graph for a fixed input shape: the kernels replay back to back without
+    per-launch host work.  `module` is one `FlashMoE` layer or any eval-mode module built from such layers whose
+    forward maps hidden states to ``(output, router_logits)`` - e.g. a `FlashMoEStack`, whose eight layers then
+    replay as one graph.  Write the input into ``static_input`` (or pass it to ``__call__``, which copies it there),
+    then read ``static_output`` / ``static_router_logits``; they are overwritten by the next replay.
 
-    def __init__(self, layer: FlashMoE, example: torch.Tensor, warmup: int = 3):
-        if layer.training:
+    The graph has the addresses of the layers' scratch memory baked in, so it keeps those allocations alive: a later
+    eager forward with more tokens makes a layer allocate a larger workspace of its own, never one the graph uses."""
+
+    def __init__(self, module: nn.Module, example: torch.Tensor, warmup: int = 3):
+        if module.training:
             raise _lib.FmoeError("capture the layer in eval mode (train mode updates host-side counters)")
-        self.layer = layer
+        self.layer = module
         self.static_input = example.clone()
         side = torch.cuda.Stream(device=example.device)
         side.wait_stream(torch.cuda.current_stream(example.device))
         with torch.cuda.stream(side), torch.no_grad():
-            for _ in range(warmup):
-                layer(self.static_input)
+            for _ in range(max(warmup, 1)):  # at least one eager forward: the workspaces exist before the capture
+                module(self.static_input)
         torch.cuda.current_stream(example.device).wait_stream(side)
         torch.cuda.synchronize(example.device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.no_grad(), torch.cuda.graph(self.graph):
-            self.static_output, self.static_router_logits = layer(self.static_input)
+            self.static_output, self.static_router_logits = module(self.static_input)
+        self._workspaces = [ws for m in module.modules() if isinstance(m, FlashMoE) for ws in m._workspaces.values()]
 
     def replay(self) -> None:
         self.graph.replay()

@@ -101,7 +101,7 @@ class FlashMLPFunc(torch.autograd.Function):
         dwg = torch.matmul(da.t(), x2)
         dwu = torch.matmul(db.t(), x2)
         dx = torch.addmm(torch.matmul(da, wg), db, wu)
-        return dx.view_as(x), dwg, dwu, dwd
+        return dx.reshape(x.shape), dwg, dwu, dwd
 
 
 def flash_mlp_func(x, gate_weight, up_weight, down_weight):

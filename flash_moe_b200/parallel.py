@@ -60,6 +60,40 @@ def plan_dispatch(indices: torch.Tensor, gates: torch.Tensor, num_experts: int, 
     return counts, torch.cat(tok_l), torch.cat(id_l), torch.cat(gate_l)
 
 
+class PeerLeftError(RuntimeError):
+    """Another rank of the group has announced that it left; no multi-GPU step may be launched any more."""
+
+
+class StepGuard:
+    """Host-side agreement that every rank is still there, checked BEFORE a multi-GPU step is launched.
+
+    A rank leaves only between steps, with none of its kernels or collectives in flight, and says so through the
+    key-value store of the process group (`leave()`); the others learn of it at their next `begin_step()` - on the
+    host, before any kernel or collective of that step exists - and raise `PeerLeftError` instead of waiting for a
+    peer that will never come.  A rank that dies without saying so is caught one level down, by the process group's
+    timeout on its next collective (give `init_process_group` a short `timeout`).
+    """
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "fmoe_step_guard"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+        self.step = -1
+
+    def _left_key(self, r: int) -> str:
+        return f"{self.prefix}/left/{r}"
+
+    def begin_step(self) -> int:
+        gone = [r for r in range(self.world) if r != self.rank and self.store.check([self._left_key(r)])]
+        if gone:
+            raise PeerLeftError(f"rank(s) {gone} left the group after step {self.step}; not launching step {self.step + 1}")
+        self.step += 1
+        self.store.set(f"{self.prefix}/step/{self.rank}", str(self.step))
+        return self.step
+
+    def leave(self) -> None:
+        """Call between steps, after synchronising this rank's device: announces that this rank is gone."""
+        self.store.set(self._left_key(self.rank), str(self.step))
+
+
 def _all_to_all(t: torch.Tensor, recv_rows: int, out_splits: List[int], in_splits: List[int], group) -> torch.Tensor:
     out = torch.empty((recv_rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     dist.all_to_all_single(out, t.contiguous(), out_splits, in_splits, group=group)
@@ -94,6 +128,11 @@ class ExpertShardedExperts:
         """x [T_local, H], indices [T_local, k] (global ids), gates [T_local, k] -> float32 [T_local, H]."""
         world, group = self.world, self.group
         counts, tok, ids, gts = plan_dispatch(indices, gates, self.num_experts, world)
+        # a split table that does not describe the payload would make the peers wait for rows that never come:
+        # refuse it here, on the host, before anything is posted
+        if len(counts) != world or min(counts) < 0 or sum(counts) != int(tok.numel()) or ids.shape[0] != sum(counts) \
+                or gts.shape[0] != sum(counts):
+            raise ValueError(f"dispatch plan is inconsistent: counts {counts} for {int(tok.numel())} token rows")
         send_counts = torch.tensor(counts, dtype=torch.int64, device=x.device)
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=group)

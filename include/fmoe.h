@@ -170,6 +170,14 @@ int fmoe_gather_probe(const void* table, int64_t num_rows, const int32_t* row_id
                       int ctas_per_sm, int mode, float* sink, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * Self-test of the bounded device-side waits (no counterpart in the reference): a one-thread kernel waits on a
+ * barrier that nothing completes, gives up after limit_ns (clamped to 10 ms), ORs FMOE_STATUS_WAIT_TIMEOUT into
+ * *status, writes 2 to *result (1 would mean the barrier completed) and returns; later launches work as usual.
+ * It exercises the give-up path that keeps a stuck copy or peer from hanging a shared GPU.
+ */
+int fmoe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, int32_t* result, fmoe_stream_t stream);
+
+/*
  * Combine step of the expert-sharded layout (tables split over GPUs by expert id, token rows sent to
  * the owners, partial results sent back): out[t] = sum_g rows[slot[g * num_tokens + t]], skipping
  * slot < 0, sources added in ascending g in float32.  rows [num_rows, hidden] float32 are the partial
@@ -187,11 +195,14 @@ int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t
  * gather kernels read with plain loads over NVLink - no dispatch, no all-to-all, no host planning.  Every GPU calls
  * it for its own tokens.  bf16 / fp16 only; workspace as for fmoe_expert_forward.  The reference has no multi-GPU
  * code; the result equals fmoe_expert_forward on the unsharded tables bit for bit.
+ * hot_down / hot_up (nullable, [num_hot, hidden], local memory): copies of the most frequently selected experts kept
+ * on every GPU so that their rows never cross NVLink; the caller rewrites the id of hot expert j to num_experts + j.
  */
 int fmoe_expert_forward_sharded(const void* x, const void* const* down_shards, const void* const* up_shards,
                                 int num_shards, const int64_t* indices, const void* gates, void* out, int dtype,
                                 int out_dtype, int64_t num_tokens, int hidden, int64_t num_experts, int top_k,
-                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream);
+                                void* workspace, size_t workspace_bytes, int32_t* status, fmoe_stream_t stream,
+                                const void* hot_down, const void* hot_up, int64_t num_hot);
 
 /*
  * fmoe_expert_forward without a caller-supplied workspace.  It has no counterpart in the
@@ -202,7 +213,9 @@ int fmoe_expert_forward_sharded(const void* x, const void* const* down_shards, c
  * the library holds until the process exits.  Shapes with fmoe_expert_workspace_bytes(...) above
  * that limit return FMOE_ERR_WORKSPACE.  All calls share the array: calls that overlap on the GPU
  * race, so order them on one stream or with events.  The first call on a device looks up the
- * array's device address and should be made outside any stream capture.  Nothing is allocated.
+ * array's device address (which, with CUDA's lazy module loading, may be the moment the driver
+ * loads this library's device code and the 8 MiB with it): make it during warm-up and outside any
+ * stream capture.  After that first call nothing is allocated.
  */
 size_t fmoe_expert_static_scratch_bytes(void);
 int fmoe_expert_forward_static(const void* x, const void* down, const void* up, const int64_t* indices,
@@ -238,6 +251,8 @@ int fmoe_mlp_forward_saving_preacts(const void* x, const void* gate_w, const voi
  * [2*num_keys, H], down_embed/up_embed [N, H], router_norm running buffers [H].
  * Outputs: y [T, H]; router_logits [T, 2*num_keys] (the module returns it viewed as
  * (2, T, num_keys)); optional indices [T,k] int64 and gates [T,k] for inspection.
+ * residual (nullable) is added in the last GEMM's epilogue: the reference leaves the skip connection of the
+ * surrounding decoder block to its caller (flash_moe/modules/flash_moe.py:55-59 takes **kwargs for such callers).
  * aux_stream (nullable): a second stream the shared MLP may run on concurrently with routing.
  * stage_events (nullable): host array of 2*FMOE_NUM_STAGES cudaEvent_t handles; entry 2*s is
  * recorded before and 2*s+1 after stage s (enum fmoe_stage) on the stream that stage runs on,
@@ -286,6 +301,8 @@ typedef struct fmoe_layer_args {
   float bn_eps;
   const float* bn_global_sums; /* nullable; training only: [2*H] sums over all shards (fmoe_bn_batch_sums) */
   int64_t bn_global_count;     /* rows behind bn_global_sums */
+  const void* residual;        /* nullable: [T, H] in `dtype`; y = dtype(shared MLP + experts + residual), the
+                                  caller's `x + layer(x)` (a decoder block's skip connection) with ONE rounding */
 } fmoe_layer_args;
 
 size_t fmoe_layer_workspace_bytes(int64_t num_tokens, int hidden, int intermediate, int64_t num_experts, int num_keys,

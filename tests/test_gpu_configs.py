@@ -126,6 +126,13 @@ def test_config5_stack_shapes(layers, B, S):
                            dt, 2e-2)
             g = layer.last_gates.float().sum(-1)
             assert (g - 1).abs().max().item() < 2e-2  # renormalised gates
-            cur = cur + y
+            # the stack hands the skip connection to the layer, which adds it before its single rounding:
+            # same routing, and within one rounding of the two-step `cur + y`
+            nxt, logits_r = layer(cur, residual=cur)
+            assert torch.equal(logits_r, logits)
+            exact_two_step = cur.float() + y.float()
+            tol = 2.0 ** -7 * torch.maximum(y.float().abs(), nxt.float().abs()) + 1e-6
+            assert ((nxt.float() - exact_two_step).abs() <= tol).all()
+            cur = nxt
         final, _ = stack(x.cuda())
     assert torch.equal(final, cur)

@@ -102,3 +102,89 @@ def test_expert_sharded_dispatch_combine_two_gloo_ranks(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("ok") == 2
+
+
+FAILURE_WORKER = textwrap.dedent(
+    """
+    import datetime, os, sys, time, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["FMOE_ROOT"])
+    import flash_moe_b200.parallel as P
+    from oracle import flashmoe_oracle as O
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=8))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    store = dist.distributed_c10d._get_default_store()
+    mode = os.environ["FMOE_FAILURE"]
+    g = torch.Generator().manual_seed(5)
+    T, H, N, k = 16, 8, 32, 3
+    x = torch.randn(T, H, generator=g)
+    down, up = torch.randn(N, H, generator=g), torch.randn(N, H, generator=g)
+    idx = torch.randint(0, N, (T, k), generator=g)
+    gates = torch.softmax(torch.randn(T, k, generator=g), -1)
+    s, e = P.token_shard(T, rank, world)
+
+    def combine(rows, slot, ntok):
+        out = torch.zeros(ntok, rows.shape[1])
+        for g_ in range(slot.shape[0]):
+            m = slot[g_] >= 0
+            out[m] += rows[slot[g_][m].long()]
+        return out
+
+    layer = P.ExpertShardedExperts(P.shard_expert_table(down, rank, world), P.shard_expert_table(up, rank, world), N,
+                                   expert_fn=O.expert_forward, combine_fn=combine)
+    guard = P.StepGuard(store, rank, world)
+    guard.begin_step()
+    layer.forward(x[s:e], idx[s:e], gates[s:e])  # step 0 works on every rank
+    dist.barrier()
+    if mode == "bad_split_table":
+        if rank == 1:
+            real = P.plan_dispatch
+            def broken(*a, **kw):  # announces one row more than it holds
+                counts, tok, ids, gts = real(*a, **kw)
+                counts[0] += 1
+                return counts, tok, ids, gts
+            P.plan_dispatch = broken
+        t0 = time.time()
+        try:
+            guard.begin_step()
+            layer.forward(x[s:e], idx[s:e], gates[s:e])
+            print("rank", rank, "UNEXPECTED success")
+        except ValueError as err:
+            print("rank", rank, "refused its own plan:", str(err)[:60])
+        except Exception as err:  # the healthy rank: its collective ends with an error after the group's timeout
+            print("rank", rank, "collective failed after %.0f s: %s" % (time.time() - t0, type(err).__name__))
+        os._exit(0)
+    if mode == "rank_leaves":
+        if rank == 1:
+            guard.leave()  # between steps, nothing in flight
+            print("rank", rank, "left")
+            os._exit(0)
+        store.wait([guard._left_key(1)], datetime.timedelta(seconds=8))
+        try:
+            guard.begin_step()
+            print("rank", rank, "UNEXPECTED launch")
+        except P.PeerLeftError as err:
+            print("rank", rank, "did not launch:", str(err)[:50])
+        os._exit(0)
+    """
+)
+
+
+@pytest.mark.parametrize("mode", ["bad_split_table", "rank_leaves"])
+def test_failures_are_reported_on_the_host_instead_of_waited_for(tmp_path, mode):
+    """Two gloo ranks: (a) a rank whose split table does not describe its payload refuses to post it, and the
+    healthy rank's collective ends with an error after the group's short timeout instead of blocking for ever;
+    (b) a rank that leaves between steps is noticed by the other on the host, before it launches the next step."""
+    script = tmp_path / "failure_worker.py"
+    script.write_text(FAILURE_WORKER)
+    env = dict(os.environ, FMOE_ROOT=ROOT, OMP_NUM_THREADS="1", FMOE_FAILURE=mode)
+    port = "29735" if mode == "bad_split_table" else "29737"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", port, str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    out = res.stdout + res.stderr
+    assert "UNEXPECTED" not in out, out[-3000:]
+    if mode == "bad_split_table":
+        assert "rank 1 refused its own plan" in out, out[-3000:]
+        assert "rank 0 collective failed" in out, out[-3000:]
+    else:
+        assert "rank 1 left" in out and "rank 0 did not launch" in out, out[-3000:]
