@@ -437,7 +437,7 @@ def record_c4(dev, peaks, flush, world, rank):
     import torch.distributed as dist
 
     from flash_moe_b200.ops.flash_expert import flash_expert_func
-    from flash_moe_b200.parallel import ExpertShardedExperts, PeerShardedExperts, token_shard
+    from flash_moe_b200.parallel import ExpertShardedExperts, PeerShardedExperts, choose_hot_experts, token_shard
 
     T, H, N, k = C4["T"], C4["H"], C4["N"], C4["k"]
     dt = torch.bfloat16
@@ -481,19 +481,44 @@ def record_c4(dev, peaks, flush, world, rank):
     peer.up_shard.copy_(up)
     peer.publish()
     ms = cuda_time(lambda: peer.forward(x, idx, gates), 5, flush)
-    remote = 2.0 * 2 * (e - s) * k * H * (world - 1) / world
-    rec["peer_sharded"] = finish(ms, {"nvlink_bytes_per_rank": remote,
-                                      "nvlink_gbs_per_rank": round(remote / (ms * 1e-3) / 1e9, 1),
-                                      "limiter": "NVLink: every remote row crosses it once (measured peer copy 770 GB/s per direction)"})
+
+    def remote_bytes(hot_ids):
+        far = (idx % world) != rank
+        if hot_ids is not None:
+            far = far & ~torch.isin(idx, hot_ids)
+        return 2.0 * 2 * float(far.sum()) * H
+
+    remote = remote_bytes(None)
+    limiter = "NVLink: every remote row crosses it once (measured peer copy 770 GB/s per direction)"
+    rec["peer_sharded"] = finish(ms, {"nvlink_bytes_per_rank": remote, "limiter": limiter,
+                                      "nvlink_gbs_per_rank": round(remote / (ms * 1e-3) / 1e9, 1)})
+    # the 256 most popular experts of this batch copied to every GPU: their rows no longer cross NVLink
+    hot = choose_hot_experts(idx, N, 256)
+    peer.replicate_hot_experts(hot)
+    ms = cuda_time(lambda: peer.forward(x, idx, gates), 5, flush)
+    remote = remote_bytes(hot)
+    pairs_hot = float(torch.isin(idx, hot).float().mean())
+    rec["peer_sharded_hot256"] = finish(ms, {"nvlink_bytes_per_rank": remote, "limiter": limiter,
+                                             "nvlink_gbs_per_rank": round(remote / (ms * 1e-3) / 1e9, 1),
+                                             "share_of_pairs_on_replicated_experts": round(pairs_hot, 3)})
     del peer
     # ---- all-to-all form: token rows to the owners, partial rows back
     a2a = ExpertShardedExperts(down, up, N)
     ms = cuda_time(lambda: a2a.forward(x, idx, gates), 5, flush)
-    st = a2a.last_stats
-    rec["all_to_all"] = finish(ms, {"dispatch_bytes_per_rank": st.get("dispatch_bytes"),
-                                    "combine_bytes_per_rank": st.get("combine_bytes"),
-                                    "rows_sent": st.get("sent_rows"), "rows_received": st.get("received_rows"),
-                                    "replicated_hot_experts": st.get("hot_experts", 0)})
+
+    def a2a_stats():
+        st = a2a.last_stats
+        moved = (st.get("dispatch_bytes") or 0) + (st.get("combine_bytes") or 0)
+        return {"dispatch_bytes_per_rank": st.get("dispatch_bytes"), "combine_bytes_per_rank": st.get("combine_bytes"),
+                "rows_sent": st.get("sent_rows"), "rows_received": st.get("received_rows"),
+                "replicated_hot_experts": st.get("hot_experts", 0), "collectives": st.get("collectives"),
+                "limiter": "NVLink payload (dispatch + float32 partial rows back) plus one host read of the count matrix",
+                "nvlink_bytes_per_rank": moved}
+
+    rec["all_to_all"] = finish(ms, a2a_stats())
+    a2a.replicate_hot_experts(hot)
+    ms = cuda_time(lambda: a2a.forward(x, idx, gates), 5, flush)
+    rec["all_to_all_hot256"] = finish(ms, a2a_stats())
     return rec
 
 
@@ -580,7 +605,8 @@ def multi_gpu_check(dev, rank, world):
 
     from flash_moe_b200 import FlashMoE, FlashMoEConfig, check_status
     from flash_moe_b200.ops.flash_expert import flash_expert_fp32, flash_expert_func
-    from flash_moe_b200.parallel import ExpertShardedExperts, PeerShardedExperts, shard_expert_table, token_shard
+    from flash_moe_b200.parallel import (ExpertShardedExperts, PeerShardedExperts, choose_hot_experts,
+                                         shard_expert_table, token_shard)
 
     out = {}
     dt = torch.bfloat16
@@ -629,6 +655,12 @@ def multi_gpu_check(dev, rank, world):
     if not err < 1e-5:
         raise RuntimeError(f"multi_gpu_check: all-to-all experts differ from the unsharded op ({err:.2e})")
     out["all_to_all_experts_equal_unsharded"] = "ok"
+    hot = choose_hot_experts(idx[s:e], N, 32)
+    a2a.replicate_hot_experts(hot)
+    got = a2a.forward(xs[s:e], idx[s:e], gates[s:e])
+    err = (got - want32[s:e]).abs().max().item() / want32.abs().max().item()
+    if not err < 1e-5:
+        raise RuntimeError(f"multi_gpu_check: all-to-all experts with replicated hot experts differ ({err:.2e})")
     peer = PeerShardedExperts(N, H, dt, dev)
     peer.down_shard.copy_(shard_expert_table(down, rank, world))
     peer.up_shard.copy_(shard_expert_table(up, rank, world))
@@ -638,6 +670,12 @@ def multi_gpu_check(dev, rank, world):
     if not torch.equal(got16, want16[s:e]):
         raise RuntimeError("multi_gpu_check: peer-sharded experts differ from the unsharded op")
     out["peer_sharded_experts_bit_equal_unsharded"] = "ok"
+    peer.replicate_hot_experts(hot)
+    got16 = peer.forward(xs[s:e], idx[s:e], gates[s:e])
+    torch.cuda.synchronize(dev)
+    if not torch.equal(got16, want16[s:e]):
+        raise RuntimeError("multi_gpu_check: peer-sharded experts with replicated hot experts differ")
+    out["hot_expert_replication_keeps_results"] = "ok"
     check_status()
     dist.barrier()
     return out

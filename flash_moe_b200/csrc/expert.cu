@@ -600,7 +600,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
                                         static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act,
-                                        nullptr, 1, raw_out);
+                                        nullptr, 1, raw_out, 0);
       FMOE_LAUNCH_CHECK();
     }
     return FMOE_OK;

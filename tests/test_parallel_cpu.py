@@ -9,7 +9,7 @@ import textwrap
 import pytest
 import torch
 
-from flash_moe_b200.parallel import plan_dispatch, shard_expert_table, token_shard
+from flash_moe_b200.parallel import plan_dispatch_device, shard_expert_table, token_shard
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -26,30 +26,23 @@ def test_token_shard_covers_all_rows_once():
         token_shard(10, 2, 2)
 
 
-def test_plan_dispatch_sends_each_token_once_per_owner():
+def test_device_plan_marks_each_token_once_per_owner():
     g = torch.Generator().manual_seed(0)
     T, k, N, world = 50, 6, 40, 4
     idx = torch.randint(0, N, (T, k), generator=g)
     idx[3, 2] = -1
     idx[4, 0] = N  # out of range: dropped
-    gates = torch.rand(T, k, generator=g)
-    counts, tok, ids, gts = plan_dispatch(idx, gates, N, world)
-    assert sum(counts) == tok.numel() == ids.shape[0] == gts.shape[0]
-    off = 0
-    total_pairs = 0
-    for dest, c in enumerate(counts):
-        t = tok[off : off + c]
-        assert t.unique().numel() == c  # one row per (token, destination)
-        for row, token in enumerate(t.tolist()):
-            mine = [(int(e) // world, float(w)) for e, w in zip(idx[token], gates[token]) if 0 <= e < N and e % world == dest]
-            got = [(int(e), float(w)) for e, w in zip(ids[off + row], gts[off + row]) if w != 0]
-            assert sorted(mine) == sorted(got)
-            # the other slots are empty: id -1, gate 0
-            assert {int(e) for e in ids[off + row]} - {-1} == {e for e, _ in mine}
-            assert all(float(w) == 0 for e, w in zip(ids[off + row], gts[off + row]) if int(e) == -1)
-            total_pairs += len(mine)
-        off += c
-    assert total_pairs == int(((idx >= 0) & (idx < N)).sum())
+    skip = torch.zeros(T, k, dtype=torch.bool)
+    skip[5, 1] = True  # a slot served from replicated rows does not travel
+    member, dest, local, live = plan_dispatch_device(idx, N, world, skip)
+    assert member.shape == (T, world) and not live[3, 2] and not live[4, 0] and not live[5, 1]
+    for t in range(T):
+        owners = {int(e) % world for j, e in enumerate(idx[t]) if 0 <= e < N and not skip[t, j]}
+        assert {g_ for g_ in range(world) if member[t, g_]} == owners
+        for j in range(k):
+            if live[t, j]:
+                assert int(dest[t, j]) == int(idx[t, j]) % world and int(local[t, j]) == int(idx[t, j]) // world
+    assert int(live.sum()) == int(((idx >= 0) & (idx < N)).sum()) - 1
     table = torch.arange(N).unsqueeze(1).float()
     assert torch.equal(shard_expert_table(table, 1, world)[:, 0], torch.arange(1, N, world).float())
 
@@ -86,6 +79,16 @@ WORKER = textwrap.dedent(
     err = (got - want[s:e]).abs().max().item()
     assert err < 1e-5, err
     assert layer.last_stats["sent_rows"] <= (e - s) * min(k, world)
+    sent_before = layer.last_stats["sent_rows"]
+    # the hottest experts replicated on every rank: same result, fewer rows on the wire
+    from flash_moe_b200.parallel import choose_hot_experts
+    hot = choose_hot_experts(idx[s:e], N, 8)
+    assert hot.numel() == 8 and 0 in hot.tolist()  # Zipf: id 0 is the most popular expert
+    layer.replicate_hot_experts(hot)
+    got = layer.forward(x[s:e], idx[s:e], gates[s:e])
+    err = max(err, (got - want[s:e]).abs().max().item())
+    assert err < 1e-5, err
+    assert layer.last_stats["sent_rows"] <= sent_before and layer.last_stats["hot_experts"] == 8
     dist.barrier()
     dist.destroy_process_group()
     print("rank", rank, "ok", err)
@@ -114,6 +117,10 @@ FAILURE_WORKER = textwrap.dedent(
     rank, world = dist.get_rank(), dist.get_world_size()
     store = dist.distributed_c10d._get_default_store()
     mode = os.environ["FMOE_FAILURE"]
+
+    def say(*parts):  # one write per line, so the two ranks' lines cannot interleave
+        os.write(1, (" ".join(str(p_) for p_ in parts) + "\\n").encode())
+
     g = torch.Generator().manual_seed(5)
     T, H, N, k = 16, 8, 32, 3
     x = torch.randn(T, H, generator=g)
@@ -136,55 +143,62 @@ FAILURE_WORKER = textwrap.dedent(
     layer.forward(x[s:e], idx[s:e], gates[s:e])  # step 0 works on every rank
     dist.barrier()
     if mode == "bad_split_table":
-        if rank == 1:
-            real = P.plan_dispatch
-            def broken(*a, **kw):  # announces one row more than it holds
-                counts, tok, ids, gts = real(*a, **kw)
-                counts[0] += 1
-                return counts, tok, ids, gts
-            P.plan_dispatch = broken
-        t0 = time.time()
+        # rank 1 comes with rows of another layout (fewer slots per token): every rank sees it in the gathered
+        # table and refuses on the host; no payload is posted, nobody waits
+        kk = k - 1 if rank == 1 else k
         try:
             guard.begin_step()
-            layer.forward(x[s:e], idx[s:e], gates[s:e])
-            print("rank", rank, "UNEXPECTED success")
+            layer.forward(x[s:e], idx[s:e, :kk], gates[s:e, :kk])
+            say("rank", rank, "UNEXPECTED success")
         except ValueError as err:
-            print("rank", rank, "refused its own plan:", str(err)[:60])
-        except Exception as err:  # the healthy rank: its collective ends with an error after the group's timeout
-            print("rank", rank, "collective failed after %.0f s: %s" % (time.time() - t0, type(err).__name__))
+            say("rank", rank, "refused the exchange:", str(err)[:40])
+        os._exit(0)
+    if mode == "rank_dies":
+        # rank 1 dies without a word before the step's first collective: the short timeout of the process group
+        # ends rank 0's collective with an error instead of blocking it for ever
+        if rank == 1:
+            os._exit(0)
+        t0 = time.time()
+        try:
+            layer.forward(x[s:e], idx[s:e], gates[s:e])
+            say("rank", rank, "UNEXPECTED success")
+        except Exception as err:
+            say("rank", rank, "collective failed after %.0f s: %s" % (time.time() - t0, type(err).__name__))
         os._exit(0)
     if mode == "rank_leaves":
         if rank == 1:
             guard.leave()  # between steps, nothing in flight
-            print("rank", rank, "left")
+            say("rank", rank, "left")
             os._exit(0)
         store.wait([guard._left_key(1)], datetime.timedelta(seconds=8))
         try:
             guard.begin_step()
-            print("rank", rank, "UNEXPECTED launch")
+            say("rank", rank, "UNEXPECTED launch")
         except P.PeerLeftError as err:
-            print("rank", rank, "did not launch:", str(err)[:50])
+            say("rank", rank, "did not launch:", str(err)[:50])
         os._exit(0)
     """
 )
 
 
-@pytest.mark.parametrize("mode", ["bad_split_table", "rank_leaves"])
+@pytest.mark.parametrize("mode", ["bad_split_table", "rank_dies", "rank_leaves"])
 def test_failures_are_reported_on_the_host_instead_of_waited_for(tmp_path, mode):
-    """Two gloo ranks: (a) a rank whose split table does not describe its payload refuses to post it, and the
-    healthy rank's collective ends with an error after the group's short timeout instead of blocking for ever;
-    (b) a rank that leaves between steps is noticed by the other on the host, before it launches the next step."""
+    """Two gloo ranks: (a) a rank that announces rows of another layout is refused by every rank on the host, before
+    any payload is posted; (b) a rank that dies silently makes the other's collective end with an error after the
+    group's short timeout instead of blocking for ever; (c) a rank that leaves between steps is noticed by the other
+    on the host, before it launches the next step."""
     script = tmp_path / "failure_worker.py"
     script.write_text(FAILURE_WORKER)
     env = dict(os.environ, FMOE_ROOT=ROOT, OMP_NUM_THREADS="1", FMOE_FAILURE=mode)
-    port = "29735" if mode == "bad_split_table" else "29737"
+    port = {"bad_split_table": "29735", "rank_dies": "29736", "rank_leaves": "29737"}[mode]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", port, str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     out = res.stdout + res.stderr
     assert "UNEXPECTED" not in out, out[-3000:]
     if mode == "bad_split_table":
-        assert "rank 1 refused its own plan" in out, out[-3000:]
+        assert "rank 0 refused the exchange" in out and "rank 1 refused the exchange" in out, out[-3000:]
+    elif mode == "rank_dies":
         assert "rank 0 collective failed" in out, out[-3000:]
     else:
         assert "rank 1 left" in out and "rank 0 did not launch" in out, out[-3000:]
