@@ -598,6 +598,77 @@ def cublas_same_shapes(dev, flush):
             "note": "library GEMMs only: no batch-norm, activation, addend or rounding fused; L2 flushed between calls"}
 
 
+def training_step_record(dev, steps=20, graph=True):
+    """Backward of the expert op alone, expert forward + backward, and one full training step of the layer (forward
+    + backward through autograd, eager and replayed from one CUDA graph) at the benchmark workload; CUDA-event
+    means over back-to-back iterations, inputs resident on the GPU."""
+    from flash_moe_b200 import FlashMoE, FlashMoEConfig, check_status
+    from flash_moe_b200.ops.flash_expert import _expert_backward, flash_expert_func
+
+    w = WORKLOAD
+    T, H, I, N, k = w["T"], w["H"], w["I"], w["N"], w["k"]
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    with torch.enable_grad():
+        torch.manual_seed(0)
+        layer = FlashMoE(FlashMoEConfig(H, I, "silu", N, k, False)).to(torch.bfloat16).to(dev).eval()
+        g = torch.Generator(device=dev).manual_seed(1)
+        x = torch.randn(1, T, H, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+        dy = torch.randn(1, T, H, device=dev, generator=g).to(torch.bfloat16)
+        idx = torch.randint(0, N, (T, k), device=dev, generator=g)
+        gates = torch.softmax(torch.randn(T, k, device=dev, generator=g), -1).to(torch.bfloat16)
+        xf, do = x.detach().view(T, H), dy.view(T, H)
+        down, up = layer.down_embed.weight.detach(), layer.up_embed.weight.detach()
+        out = {"workload": w["name"] + ", gradients of x and every parameter", "steps": steps}
+        out["expert_backward_ms"] = round(timed(lambda: _expert_backward(do, xf, down, up, idx, gates)), 4)
+
+        def expert_step():
+            leaves = [t.detach().requires_grad_() for t in (xf, down, up, gates)]
+            flash_expert_func(leaves[0], leaves[1], leaves[2], idx, leaves[3]).backward(do)
+
+        out["expert_forward_backward_ms"] = round(timed(expert_step), 4)
+
+        def layer_step():
+            for p in layer.parameters():
+                p.grad = None
+            x.grad = None
+            y, _ = layer(x)
+            y.backward(dy)
+
+        out["layer_forward_backward_ms"] = round(timed(layer_step), 4)
+        best = out["layer_forward_backward_ms"]
+        if graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                layer_step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            for p in layer.parameters():
+                p.grad = None
+            x.grad = None
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                y, _ = layer(x)
+                y.backward(dy)
+            out["layer_forward_backward_graph_ms"] = round(timed(cg.replay), 4)
+            best = min(best, out["layer_forward_backward_graph_ms"])
+    check_status()
+    out["tokens_per_s_training_step"] = T / (best * 1e-3)
+    return out
+
+
 def multi_gpu_check(dev, rank, world):
     """Small-shape correctness checks of every multi-GPU path, run by all ranks before the timed region; raises on a
     mismatch.  (NVLS is off for this process and the peer path uses plain peer loads.)"""
@@ -693,6 +764,9 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="(default) run the shared MLP on the main stream")
     ap.add_argument("--overlap", action="store_true", help="fork the shared-MLP up GEMM to a side stream")
     ap.add_argument("--eager", action="store_true", help="time plain module calls instead of CUDA-graph replays")
+    ap.add_argument("--only", default=None, choices=["training_step", "training_step_eager", "layer_forward"],
+                    help="run just this piece (what the ncu summaries under profiles/ were captured on): the training "
+                         "step sub-record, or three eager forwards of the benchmark layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -702,6 +776,23 @@ def main():
     if args.impl == "reference-gpu":
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(reference_gpu_record(args.steps, args.warmup)))
+        return
+
+    if args.only == "layer_forward":
+        from flash_moe_b200 import check_status
+
+        layer, x = build_inputs(torch.bfloat16)
+        layer, x = layer.cuda(), x.cuda()
+        with torch.no_grad():
+            for _ in range(3):
+                layer(x)
+        torch.cuda.synchronize()
+        check_status()
+        print(json.dumps({"only": "layer_forward", "forwards": 3, "workload": WORKLOAD["name"]}))
+        return
+    if args.only is not None:
+        torch.cuda.set_device(0)
+        print(json.dumps(training_step_record(torch.device("cuda", 0), args.steps, graph=args.only == "training_step")))
         return
 
     import torch.distributed as dist
@@ -942,7 +1033,7 @@ def main():
             return
         emitted.set()
         if extras:
-            for key in ("sustained", "cublas_same_shape_ms", "reference_gpu"):
+            for key in ("sustained", "cublas_same_shape_ms", "reference_gpu", "training_step"):
                 if key in extras:
                     line[key] = extras.pop(key)
             if extras:
@@ -988,6 +1079,7 @@ def main():
         guarded("sustained", lambda: sustained_record(graphed, dev, local, T, world))
     guarded("cublas_same_shape_ms", lambda: cublas_same_shapes(dev, flush))
     del e2e_graphs, graphed
+    guarded("training_step", lambda: training_step_record(dev))
     guarded("c3", lambda: record_c3(dev, peaks, flush))
     guarded("c4", lambda: record_c4(dev, peaks, flush, world, rank), collective=world > 1)
     guarded("c5", lambda: record_c5(dev, peaks, world, rank), collective=world > 1)

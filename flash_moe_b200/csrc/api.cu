@@ -378,8 +378,8 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   FMOE_MARK(FMOE_STAGE_ROUTER_FRONT, 1, s);
 
   // shared MLP, first half: h = silu(x Wg^T) * (x Wu^T).  It is independent of routing; on the side
-  // stream it is forked AFTER the router GEMM (both want a whole SM's shared memory) so that the
-  // tensor-core GEMM overlaps the latency-bound top-k and expert gathers that follow.
+  // stream it is forked AFTER the router GEMM (both want a whole SM's shared memory and its tensor memory) so that
+  // the tensor-core GEMM overlaps the issue-bound top-k that follows.
   ForkJoin* fj = nullptr;
   // after the fork every early return first joins the side stream back into the caller's, so that a failed call
   // never leaves a dangling branch (which would also invalidate a stream capture in progress)
@@ -416,6 +416,17 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   }
   if (rc != FMOE_OK) return fail(rc);
   FMOE_MARK(FMOE_STAGE_ROUTER_TOPK, 1, s);
+  // The side stream is joined HERE, before the experts: the two gather passes compete with the GEMM for the same
+  // L2 -> SM bandwidth and are slower beside it than after it.  (Measured at the benchmark shape the fork does not
+  // pay either way - 230 vs 226 us: the top-k's CTAs fill the shared memory first and the GEMM's wait for them; with
+  // the top-k held to one CTA per SM so that the GEMM fits beside it, the top-k itself takes 165 us, because one
+  // token costs a warp about 20 us of dependent instructions and all 4096 tokens must be resident at once.)
+  bool joined = false;
+  if (fj != nullptr) {
+    if (cudaStreamWaitEvent(s, fj->join, 0) != cudaSuccess) return fail(-static_cast<int>(cudaErrorUnknown));
+    fj = nullptr;
+    joined = true;
+  }
   FMOE_MARK(FMOE_STAGE_EXPERT_SCORES, 0, s);
 
   // routed experts into an fp32 accumulator; the scores stage ends and the accumulate stage starts
@@ -434,10 +445,7 @@ int fmoe_layer_forward(const fmoe_layer_args* a) {
   if (rc != FMOE_OK) return fail(rc);
   FMOE_MARK(FMOE_STAGE_EXPERT_ACCUM, 1, s);
 
-  if (fj != nullptr) {
-    FMOE_CUDA_TRY(cudaStreamWaitEvent(s, fj->join, 0));
-    fj = nullptr;  // joined
-  } else {
+  if (!joined) {
     FMOE_MARK(FMOE_STAGE_MLP_UP, 0, s);
     rc = mlp_up(a->x, a->gate_proj, a->up_proj, w.h, dtype, T, H, I, a->status, s);
     if (rc != FMOE_OK) return fail(rc);
