@@ -367,7 +367,9 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
 
 // ---------------------------------------------------------------- 3. per-token accumulate
 // One warp per (token, column block of 32*VEC*NCH elements); 16 x 16 B of gathered rows in flight
-// per lane, packed f32x2 FMAs (two accumulators per instruction).
+// per lane, packed f32x2 FMAs (two accumulators per instruction).  The launch bound keeps the kernel at 120
+// registers so that four CTAs (not three) fit an SM: a third more gathers in flight, 52 -> 48 us at the benchmark
+// shape (a fifth CTA would need spills and is slower: 120 vs 105 us for both passes).
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -381,7 +383,7 @@ __device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t a, uint64_t b) {
 }
 
 template <typename T, typename OutT, int NCH, bool PEER = false>
-__global__ void __launch_bounds__(128) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
+__global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restrict__ up, const int64_t* __restrict__ idx,
                                                           const float* __restrict__ gs, OutT* __restrict__ out,
                                                           int64_t ntok, int H, int64_t N, int k, int colblocks,
                                                           const T* const* __restrict__ shards = nullptr,

@@ -112,6 +112,15 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Consumer-side wait: only the first consumer warp polls the mbarrier; the other seven sleep in a hardware barrier
+// (bar.sync costs no issue slots while blocked) and are released together with it.  With all eight warps polling,
+// about half of the kernel's issued instructions were polls; removing them did not change the kernel's duration,
+// which is set by the in-order hand-over of ring slots, not by issue slots.
+__device__ __forceinline__ void consumer_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int warp) {
+  if (warp == 0) ring_wait(bar, parity, abort_flag);
+  asm volatile("bar.sync 2, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
 template <typename T> struct MmaK16;
 template <> struct MmaK16<__nv_bfloat16> {
   static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -269,7 +278,7 @@ expert_fused_kernel(const T* __restrict__ x, const T* __restrict__ down, const T
     for (int64_t t = blockIdx.x; t < ntok; t += gridDim.x, ++ti) {
       const int b = ti & 1u;
       // this warp's slice of the token's x row, as B fragments
-      ring_wait(xfull_bar(b), (ti >> 1) & 1u, abort_flag);
+      consumer_wait(xfull_bar(b), (ti >> 1) & 1u, abort_flag, warp);
       uint4 xf[NB];
 #pragma unroll
       for (int i = 0; i < NB; ++i) {
@@ -310,7 +319,7 @@ expert_fused_kernel(const T* __restrict__ x, const T* __restrict__ down, const T
 #pragma unroll 1
         for (int gi = 0; gi < ng; ++gi, ++q) {
           const int s = q % groups;
-          ring_wait(full_bar(s), (q / groups) & 1u, abort_flag);
+          consumer_wait(full_bar(s), (q / groups) & 1u, abort_flag, warp);
           const uint32_t ra = ring + s * group_bytes + g * stride;
           const uint32_t rb = ra + 8 * stride;
           float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -361,7 +370,7 @@ expert_fused_kernel(const T* __restrict__ x, const T* __restrict__ down, const T
           const int nrows = min(kGroupRows, n - gi * kGroupRows);
           const float sel = gi < 2 ? gs_lo : gs_hi;
           const int src0 = (gi & 1) * kGroupRows;
-          ring_wait(full_bar(s), (q / groups) & 1u, abort_flag);
+          consumer_wait(full_bar(s), (q / groups) & 1u, abort_flag, warp);
           const uint32_t base = ring + s * group_bytes + (warp * 128 + 4 * lane) * 2;
           // batches of 8 rows: all their shared-memory loads are issued before the first multiply-add, so the
           // load latency is paid once per batch and not once per row
