@@ -267,7 +267,8 @@ __device__ __forceinline__ const T* table_row(const T* table, const T* const* sh
 }
 
 // One warp per (token, group of 16 of its experts).  The token's x row is parked in the warp's
-// slice of shared memory (read back as B fragments right before each MMA), so every register that
+// slice of shared memory (read back as B fragments right before each MMA; fetched with cp.async one task ahead,
+// together with the next task's expert ids), so every register that
 // waits for data waits for a gathered down row: batches of UNROLL 32-column blocks (2 * UNROLL x 16 B per lane) in
 // STAGES register buffers keep gathers in flight across batches to cover the L2 latency (measured at the
 // benchmark shape: 4 x 2 buffers 57.7 us, 8 x 1 61.9 us, 4 x 3 62.6 us, 2 x 2 57.8 us).
@@ -283,33 +284,57 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
   extern __shared__ uint4 xs_all[];
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
-  uint4* xs = xs_all + (threadIdx.x >> 5) * xs_stride;  // xs_stride uint4 per warp, >= ceil(H/256)*32
+  // two x-row buffers per warp (xs_stride uint4 each, >= ceil(H/256)*32): while one task is computed, the next
+  // task's ids and x row are already on their way (cp.async), so a task does not start with an exposed round trip
+  uint4* xs_buf = xs_all + (threadIdx.x >> 5) * 2 * xs_stride;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int groups = (k + 15) >> 4;
   const int64_t tasks = ntok * groups;
   const int hv = H >> 3;  // 16-byte pieces per row
   bool bad = false;
-  int64_t t_in_smem = -1;
+  auto fetch_ids = [&](int64_t task_, int64_t& ea_, int64_t& eb_) {
+    const int64_t t_ = task_ / groups;
+    const int ja_ = static_cast<int>(task_ - t_ * groups) * 16 + g, jb_ = ja_ + 8;
+    ea_ = ja_ < k ? idx[t_ * k + ja_] : 0;
+    eb_ = jb_ < k ? idx[t_ * k + jb_] : 0;
+  };
+  auto fetch_x = [&](int64_t t_, uint4* dst) {
+    const T* xr = x + t_ * H;
+    for (int c = lane; c < xs_stride; c += 32) {
+      if (c < hv) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst + c))),
+                     "l"(reinterpret_cast<uint64_t>(xr + c * 8))
+                     : "memory");
+      } else {
+        dst[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  int cur = 0;
+  int64_t ea_next = 0, eb_next = 0;
+  if (warp_global < tasks) {
+    fetch_ids(warp_global, ea_next, eb_next);
+    fetch_x(warp_global / groups, xs_buf);
+  }
   for (int64_t task = warp_global; task < tasks; task += warps_total) {
     const int64_t t = task / groups;
     const int G = static_cast<int>(task - t * groups);
     const int ja = G * 16 + g, jb = ja + 8;
-    int64_t ea = 0, eb = 0;
-    if (ja < k) ea = idx[t * k + ja];
-    if (jb < k) eb = idx[t * k + jb];
+    const int64_t ea = ea_next, eb = eb_next;
+    const uint4* xs = xs_buf + cur * xs_stride;
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncwarp();  // this task's x row has landed; the other buffer is free (its task is finished)
+    if (task + warps_total < tasks) {
+      fetch_ids(task + warps_total, ea_next, eb_next);
+      fetch_x((task + warps_total) / groups, xs_buf + (cur ^ 1) * xs_stride);
+    }
+    cur ^= 1;
     const bool oka = (ja < k) && ea >= 0 && ea < N;
     const bool okb = (jb < k) && eb >= 0 && eb < N;
     if ((ja < k && !oka && ea != -1) || (jb < k && !okb && eb != -1)) bad = true;  // -1: empty slot, no flag
     const T* ra = table_row<T, PEER>(down, shards, world, oka ? ea : 0, H, sharded) + 8 * tq;
     const T* rb = table_row<T, PEER>(down, shards, world, okb ? eb : 0, H, sharded) + 8 * tq;
-    if (t != t_in_smem) {  // warp-uniform
-      __syncwarp();
-      const T* xr = x + t * H;
-      for (int c = lane; c < xs_stride; c += 32) xs[c] = (c < hv) ? ldg16(xr + c * 8) : make_uint4(0, 0, 0, 0);
-      __syncwarp();
-      t_in_smem = t;
-    }
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     auto load = [&](uint4 (&qa)[UNROLL], uint4 (&qb)[UNROLL], int c0) {
 #pragma unroll
@@ -394,6 +419,24 @@ __global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restric
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t tasks = ntok * colblocks;
+  // each lane fetches one slot's (expert id, weight) - one batch of 32 slots AHEAD of the batch being gathered,
+  // also across tasks, so that the gathers of a batch never wait for their own ids; invalid or absent slots get
+  // weight 0
+  auto fetch_slot = [&](int64_t t_, int j0_, int& e_, float& w_) {
+    e_ = 0;
+    w_ = 0.f;
+    const int j = j0_ + lane;
+    if (j < k) {
+      const int64_t e = idx[t_ * k + j];
+      if (e >= 0 && e < N) {
+        e_ = static_cast<int>(e);
+        w_ = gs[t_ * k + j];
+      }
+    }
+  };
+  int e_next = 0;
+  float w_next = 0.f;
+  if (warp_global < tasks) fetch_slot(warp_global / colblocks, 0, e_next, w_next);
   for (int64_t task = warp_global; task < tasks; task += warps_total) {
     const int64_t t = task / colblocks;
     const int cb = static_cast<int>(task - t * colblocks);
@@ -408,17 +451,10 @@ __global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restric
       for (int i = 0; i < VEC / 2; ++i) acc[c][i] = 0ull;
 
     for (int j0 = 0; j0 < k; j0 += 32) {
-      // each lane fetches one slot's (expert id, weight); invalid or absent slots get weight 0
-      const int j = j0 + lane;
-      int e_l = 0;
-      float w_l = 0.f;
-      if (j < k) {
-        const int64_t e = idx[t * k + j];
-        if (e >= 0 && e < N) {
-          e_l = static_cast<int>(e);
-          w_l = gs[t * k + j];
-        }
-      }
+      const int e_l = e_next;
+      const float w_l = w_next;
+      if (j0 + 32 < k) fetch_slot(t, j0 + 32, e_next, w_next);
+      else if (task + warps_total < tasks) fetch_slot((task + warps_total) / colblocks, 0, e_next, w_next);
       const int nslots = min(32, k - j0);
       auto load = [&](uint4 (&q)[SLOTS][NCH], uint64_t (&ww)[SLOTS], int s) {
 #pragma unroll
@@ -597,7 +633,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       const int64_t cap = static_cast<int64_t>(sms) * 16;
       const int grid = static_cast<int>(want < cap ? want : cap);
       const int xs_stride = ((H + 255) / 256) * 32;  // uint4 per warp, rows padded to 256 columns
-      const int smem = 4 * xs_stride * 16;
+      const int smem = 4 * 2 * xs_stride * 16;  // two x-row buffers per warp
       auto kern = expert_scores_mma_kernel<T, 4, false, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
@@ -914,7 +950,7 @@ int run_typed_peer(const void* x, const void* const* down_shards, const void* co
       const int64_t cap = static_cast<int64_t>(sms) * 16;
       const int grid = static_cast<int>(want < cap ? want : cap);
       const int xs_stride = ((H + 255) / 256) * 32;
-      const int smem = 4 * xs_stride * 16;
+      const int smem = 4 * 2 * xs_stride * 16;  // two x-row buffers per warp
       auto kern = expert_scores_mma_kernel<T, 4, true, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(x), static_cast<const T*>(hot_down), idx,

@@ -17,12 +17,10 @@
 namespace fmoe {
 namespace {
 
-constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;
 constexpr int UMMA_K = 16;
 constexpr int kXformWarps = 8;
 constexpr int kThreads = (2 + kXformWarps) * 32;
-constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
 constexpr unsigned kFull = 0xFFFFFFFFu;
 
 using epi::UmmaFmt;
@@ -32,15 +30,20 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // ring depth: 32 KB stages for 128-column tiles, 48 KB stages for 256-column tiles
 template <int BLOCK_N> struct RingDepth { static constexpr int v = BLOCK_N <= 128 ? 6 : 4; };
 
-template <int BLOCK_N, typename T>
+// BLOCK_M = 128, or 64 for small problems (twice the CTAs, half the x tile to fetch and normalise per CTA).  With
+// M = 64 the accumulator's row i sits in TMEM lane 32 * (i / 16) + i % 16: each of the four epilogue warps finds 16
+// rows in the first 16 lanes of its lane quarter.
+template <int BLOCK_M, int BLOCK_N, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       const T* __restrict__ running_mean, const T* __restrict__ running_var, float eps, T* __restrict__ out,
                       int M, int N, int K, int num_m_tiles, int num_k_blocks, int32_t* status) {
+  constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int kStages = RingDepth<BLOCK_N>::v;
+  constexpr int kPieces = BLOCK_M * 8 / 256;  // 16-byte pieces of the x tile per normalising thread
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -138,7 +141,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------ normalise the x tiles (warps 2..9)
-    // Thread i owns the 16-byte pieces i, i + 256, i + 512, i + 768 of the 128 x 128-byte tile: row (i >> 3) + 32 j,
+    // Thread i owns the 16-byte pieces i, i + 256, ... of the BLOCK_M x 128-byte tile: row (i >> 3) + 32 j,
     // position i & 7.  With the 128-byte swizzle position p of row r holds the features 8 * (p ^ (r & 7)) .. + 7 of
     // the k-block, and r & 7 does not depend on j, so one thread always handles the same eight features.
     const int xt = threadIdx.x - 64;
@@ -154,11 +157,11 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         mm[i] = v.x; ss[i] = v.y; mm[i + 1] = v.z; ss[i + 1] = v.w;
       }
       uint4* tile = reinterpret_cast<uint4*>(gen + s * STAGE_BYTES);
-      uint4 q[4];
+      uint4 q[kPieces];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) q[j] = tile[xt + 256 * j];
+      for (int j = 0; j < kPieces; ++j) q[j] = tile[xt + 256 * j];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < kPieces; ++j) {
         float f[8];
         unpack16<T>(q[j], f);
 #pragma unroll
@@ -178,8 +181,10 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (done) {
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
-        const int64_t row = static_cast<int64_t>(m_tile) * BLOCK_M + q4 * 32 + lane;
-        epi::store_add_row<T, BLOCK_N>(taddr, out + row * N, nullptr, nullptr, n_tile * BLOCK_N, N, row < M);
+        constexpr int kRowsPerWarp = BLOCK_M / 4;  // 32, or 16 (the lower half of the warp's lanes) for M = 64
+        const int64_t row = static_cast<int64_t>(m_tile) * BLOCK_M + q4 * kRowsPerWarp + lane;
+        epi::store_add_row<T, BLOCK_N>(taddr, out + row * N, nullptr, nullptr, n_tile * BLOCK_N, N,
+                                       lane < kRowsPerWarp && row < M);
       }
     }
   }
@@ -199,7 +204,7 @@ int make_map(CUtensorMap* m, const void* basep, int dtype, uint64_t cols, uint64
   return epi::make_tensor_map(m, basep, dtype, cols, rows, cols, box_rows);
 }
 
-template <int BLOCK_N, typename T>
+template <int BLOCK_M, int BLOCK_N, typename T>
 int launch_bn_gemm(const void* x, const void* w, const float* mean, const float* invstd, const void* rm, const void* rv,
                    float eps, void* out, int dtype, int64_t M, int N, int K, int32_t* status, cudaStream_t stream) {
   CUtensorMap tA, tB;
@@ -208,8 +213,8 @@ int launch_bn_gemm(const void* x, const void* w, const float* mean, const float*
   if ((rc = make_map(&tB, w, dtype, K, N, BLOCK_N)) != FMOE_OK) return rc;
   const int num_k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
   constexpr int kStages = RingDepth<BLOCK_N>::v;
-  const int smem = kStages * (A_BYTES + BLOCK_N * BLOCK_K * 2) + (3 * kStages + 1) * 8 + 24 + num_k_blocks * BLOCK_K * 8 + 1024;
-  auto kern = router_gemm_bn_kernel<BLOCK_N, T>;
+  const int smem = kStages * (BLOCK_M * BLOCK_K * 2 + BLOCK_N * BLOCK_K * 2) + (3 * kStages + 1) * 8 + 24 + num_k_blocks * BLOCK_K * 8 + 1024;
+  auto kern = router_gemm_bn_kernel<BLOCK_M, BLOCK_N, T>;
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int num_m_tiles = static_cast<int>((M + BLOCK_M - 1) / BLOCK_M);
   const int num_n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
@@ -238,16 +243,20 @@ int launch_router_bn_gemm(const void* x, const void* w, const float* mean, const
   if (running_mean == nullptr && (mean == nullptr || invstd == nullptr)) return FMOE_ERR_BAD_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(logits)) return FMOE_ERR_ALIGNMENT;
   // wide tiles once there are several waves of them: the x tile is then normalised once per 256 output columns
-  const int64_t m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
-  const bool wide = N > 128 && m_tiles * ((N + 127) / 128) >= 4 * static_cast<int64_t>(device_sm_count());
-#define FMOE_BN_GEMM(BN_)                                                                                          \
-  (dtype == FMOE_DTYPE_BF16                                                                                        \
-       ? launch_bn_gemm<BN_, __nv_bfloat16>(x, w, mean, invstd, running_mean, running_var, eps, logits, dtype, M, N, K, \
-                                            status, stream)                                                        \
-       : launch_bn_gemm<BN_, __half>(x, w, mean, invstd, running_mean, running_var, eps, logits, dtype, M, N, K,    \
-                                     status, stream))
-  if (wide) return FMOE_BN_GEMM(256);
-  return FMOE_BN_GEMM(128);
+  const int64_t m_tiles = (M + 127) / 128;
+  const int64_t tiles128 = m_tiles * ((N + 127) / 128);
+  const bool wide = N > 128 && tiles128 >= 4 * static_cast<int64_t>(device_sm_count());
+  // fewer 128 x 128 tiles than SMs: 64-row tiles put twice as many CTAs to work, each with half the x tile
+  const bool small = tiles128 < device_sm_count();
+#define FMOE_BN_GEMM(BM_, BN_)                                                                                       \
+  (dtype == FMOE_DTYPE_BF16                                                                                          \
+       ? launch_bn_gemm<BM_, BN_, __nv_bfloat16>(x, w, mean, invstd, running_mean, running_var, eps, logits, dtype, M, N, \
+                                                 K, status, stream)                                                  \
+       : launch_bn_gemm<BM_, BN_, __half>(x, w, mean, invstd, running_mean, running_var, eps, logits, dtype, M, N, K, \
+                                          status, stream))
+  if (wide) return FMOE_BN_GEMM(128, 256);
+  if (small) return FMOE_BN_GEMM(64, 128);
+  return FMOE_BN_GEMM(128, 128);
 #undef FMOE_BN_GEMM
 }
 
