@@ -279,3 +279,24 @@ def test_bounded_wait_gives_up_and_the_context_survives():
     torch.cuda.synchronize()
     check_status(dev)
     assert torch.isfinite(y.float()).all()
+
+
+def test_batch_norm_edge_cases_follow_torch():
+    """momentum=None is torch's cumulative moving average (factor 1 / batches seen); a one-row training batch raises."""
+    import torch.nn as nn
+
+    ref, ours = make_layer_pair(128, 256, 256, 4, False, torch.float32)
+    ours.train()
+    ours.router_norm.momentum = None
+    bn = nn.BatchNorm1d(128, affine=False, momentum=None)
+    xs = [randn((1, 96, 128), 40 + i) * (1.0 + 0.3 * i) + 0.2 * i for i in range(3)]
+    with torch.no_grad():
+        for x in xs:
+            ours(x.cuda())
+            bn(x.view(-1, 128))
+    torch.testing.assert_close(ours.router_norm.running_mean.cpu(), bn.running_mean, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(ours.router_norm.running_var.cpu(), bn.running_var, rtol=1e-4, atol=1e-6)
+    assert int(ours.router_norm.num_batches_tracked) == 3
+    with pytest.raises(ValueError, match="more than 1 value per channel"):
+        with torch.no_grad():
+            ours(randn((1, 1, 128), 50).cuda())

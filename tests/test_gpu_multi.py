@@ -62,6 +62,12 @@ WORKER = textwrap.dedent(
     torch.cuda.synchronize(); check_status()
     err = (got - want[s:e]).abs().max().item() / want.abs().max().item()
     assert err < 1e-5, err
+    from flash_moe_b200.parallel import choose_hot_experts
+    sharded.replicate_hot_experts(choose_hot_experts(idx[s:e], N, 64))
+    got = sharded.forward(xs[s:e], idx[s:e], gates[s:e])
+    torch.cuda.synchronize(); check_status()
+    err = max(err, (got - want[s:e]).abs().max().item() / want.abs().max().item())
+    assert err < 1e-5, err
     dist.barrier(); dist.destroy_process_group()
     print("rank", rank, "ok", err, sharded.last_stats)
     """
@@ -85,7 +91,7 @@ PEER_WORKER = textwrap.dedent(
     import os, sys, torch, torch.distributed as dist
     sys.path.insert(0, os.environ["FMOE_ROOT"])
     from flash_moe_b200 import check_status
-    from flash_moe_b200.parallel import PeerShardedExperts, shard_expert_table, token_shard
+    from flash_moe_b200.parallel import PeerShardedExperts, choose_hot_experts, shard_expert_table, token_shard
     from flash_moe_b200.ops.flash_expert import flash_expert_fp32, flash_expert_func
     rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -112,6 +118,11 @@ PEER_WORKER = textwrap.dedent(
     got16 = layer.forward(xs[s:e], idx[s:e], gates[s:e])
     torch.cuda.synchronize(); check_status()
     assert torch.equal(got32, want32[s:e]) and torch.equal(got16, want16[s:e]), "peer-sharded result differs"
+    # the most popular experts copied to every GPU: same bits, their rows no longer cross NVLink
+    layer.replicate_hot_experts(choose_hot_experts(idx[s:e], N, 64))
+    got16 = layer.forward(xs[s:e], idx[s:e], gates[s:e])
+    torch.cuda.synchronize(); check_status()
+    assert torch.equal(got16, want16[s:e]), "peer-sharded result with replicated hot experts differs"
     dist.barrier(); dist.destroy_process_group()
     print("rank", rank, "peer ok")
     """
