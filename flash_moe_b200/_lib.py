@@ -93,6 +93,7 @@ SIGNATURES = {
     "fmoe_expert_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _I, _L, _I, _P, _Z, _P, _P]),
     "fmoe_swiglu_backward": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _P]),
     "fmoe_gather_probe": (_I, [_P, _L, _P, _L, _I, _I, _I, _P, _P, _P]),
+    "fmoe_rms_norm": (_I, [_P, _P, _P, _I, _L, _I, _F, _P]),
     "fmoe_selftest_wait_timeout": (_I, [ctypes.c_uint64, _P, _P, _P]),
     "fmoe_combine_partial_rows": (_I, [_P, _L, _P, _I, _L, _I, _P, _P, _P]),
     "fmoe_expert_workspace_bytes": (_Z, [_L, _I, _L, _I]),

@@ -275,6 +275,12 @@ int fmoe_gather_probe(const void* table, int64_t num_rows, const int32_t* row_id
                              static_cast<cudaStream_t>(stream));
 }
 
+int fmoe_rms_norm(const void* x, const void* weight, void* out, int dtype, int64_t num_tokens, int hidden, float eps,
+                  fmoe_stream_t stream) {
+  if (!valid_dtype(dtype)) return FMOE_ERR_BAD_ARG;
+  return launch_rms_norm(x, weight, out, dtype, num_tokens, hidden, eps, static_cast<cudaStream_t>(stream));
+}
+
 int fmoe_combine_partial_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources,
                               int64_t num_tokens, int hidden, float* out, int32_t* status, fmoe_stream_t stream) {
   return launch_combine_rows(rows, num_rows, slot, num_sources, num_tokens, hidden, out, status,

@@ -182,6 +182,8 @@ int launch_swiglu_backward(const void* dh, const void* a, const void* b, void* d
                            int64_t n, cudaStream_t stream);
 int launch_gather_probe(const void* table, int64_t num_rows, const int32_t* row_ids, int64_t count, int row_bytes,
                         int ctas_per_sm, int mode, float* sink, int32_t* status, cudaStream_t stream);
+int launch_rms_norm(const void* x, const void* weight, void* out, int dtype, int64_t ntok, int H, float eps,
+                    cudaStream_t stream);
 int launch_combine_rows(const float* rows, int64_t num_rows, const int32_t* slot, int num_sources, int64_t ntok, int H,
                         float* out, int32_t* status, cudaStream_t stream);
 

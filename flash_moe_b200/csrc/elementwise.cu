@@ -183,6 +183,38 @@ int bn_typed(const void* x, void* xn, void* rm, void* rv, int training, float mo
   return FMOE_OK;
 }
 
+// RMS pre-norm of a decoder block in front of the layer: out[r] = T(x[r] * rsqrt(mean(x[r]^2) + eps) * weight).
+// One warp per row, float32 inside, one rounding; 16-byte loads and stores.
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ weight,
+                                                      T* __restrict__ out, int64_t ntok, int H, float eps) {
+  constexpr int VEC = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  for (int64_t r = warp_global; r < ntok; r += warps_total) {
+    const T* xr = x + r * H;
+    float ss = 0.f;
+    for (int c = lane * VEC; c < H; c += 32 * VEC) {
+      float f[VEC];
+      unpack16<T>(ldg16(xr + c), f);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ss = fmaf(f[i], f[i], ss);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(kFull, ss, d);
+    const float scale = rsqrtf(ss / static_cast<float>(H) + eps);
+    for (int c = lane * VEC; c < H; c += 32 * VEC) {
+      float f[VEC], w[VEC];
+      unpack16<T>(ldg16(xr + c), f);
+      if (weight != nullptr) unpack16<T>(ldg16(weight + c), w);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) f[i] = f[i] * scale * (weight != nullptr ? w[i] : 1.0f);
+      *reinterpret_cast<uint4*>(out + r * H + c) = pack16<T>(f);
+    }
+  }
+}
+
 // out[t] = sum over sources g of rows[slot[g * ntok + t]] (slot < 0: source g holds nothing for token t).
 // One thread per 16 bytes of an output row; sources are added in ascending g, so the sum is reproducible.
 __global__ void __launch_bounds__(256) combine_rows_kernel(const float4* __restrict__ rows, int64_t num_rows,
@@ -271,6 +303,36 @@ int launch_log_softmax_halves(const void* logits, void* log_probs, int dtype, in
       break;
     case FMOE_DTYPE_F16:
       log_softmax_halves_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(logits), static_cast<__half*>(log_probs), ntok, nk);
+      break;
+    default: return FMOE_ERR_BAD_ARG;
+  }
+  FMOE_LAUNCH_CHECK();
+  return FMOE_OK;
+}
+
+int launch_rms_norm(const void* x, const void* weight, void* out, int dtype, int64_t ntok, int H, float eps,
+                    cudaStream_t stream) {
+  if (ntok < 0 || H <= 0 || !(eps >= 0.f)) return FMOE_ERR_BAD_ARG;
+  if (ntok == 0) return FMOE_OK;
+  if (x == nullptr || out == nullptr) return FMOE_ERR_BAD_ARG;
+  if (H % (16 / dtype_size(dtype)) != 0 || !aligned16(x) || !aligned16(out) || (weight != nullptr && !aligned16(weight)))
+    return FMOE_ERR_ALIGNMENT;
+  const int64_t want = (ntok + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  switch (dtype) {
+    case FMOE_DTYPE_F32:
+      rms_norm_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<const float*>(weight),
+                                                       static_cast<float*>(out), ntok, H, eps);
+      break;
+    case FMOE_DTYPE_BF16:
+      rms_norm_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                               static_cast<const __nv_bfloat16*>(weight),
+                                                               static_cast<__nv_bfloat16*>(out), ntok, H, eps);
+      break;
+    case FMOE_DTYPE_F16:
+      rms_norm_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(weight),
+                                                        static_cast<__half*>(out), ntok, H, eps);
       break;
     default: return FMOE_ERR_BAD_ARG;
   }

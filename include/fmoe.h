@@ -170,6 +170,15 @@ int fmoe_gather_probe(const void* table, int64_t num_rows, const int32_t* row_id
                       int ctas_per_sm, int mode, float* sink, int32_t* status, fmoe_stream_t stream);
 
 /*
+ * RMS pre-norm of the decoder block that surrounds the layer: out[r] = dtype(x[r] * rsqrt(mean(x[r]^2) + eps) * weight),
+ * float32 inside, one rounding; weight (nullable) [hidden] in `dtype`.  The reference leaves normalisation to its caller
+ * (flash_moe/modules/flash_moe.py:55-59 receives already-normalised hidden states); together with the `residual`
+ * of fmoe_layer_forward this is the caller's `x + layer(norm(x))` in two library calls.
+ */
+int fmoe_rms_norm(const void* x, const void* weight, void* out, int dtype, int64_t num_tokens, int hidden, float eps,
+                  fmoe_stream_t stream);
+
+/*
  * Self-test of the bounded device-side waits (no counterpart in the reference): a one-thread kernel waits on a
  * barrier that nothing completes, gives up after limit_ns (clamped to 10 ms), ORs FMOE_STATUS_WAIT_TIMEOUT into
  * *status, writes 2 to *result (1 would mean the barrier completed) and returns; later launches work as usual.

@@ -300,3 +300,41 @@ def test_batch_norm_edge_cases_follow_torch():
     with pytest.raises(ValueError, match="more than 1 value per channel"):
         with torch.no_grad():
             ours(randn((1, 1, 128), 50).cuda())
+
+
+def test_pre_norm_stack_matches_torch_composition():
+    """Pre-norm decoder composition x <- x + layer(rms_norm(x)): the library's norm kernel against torch's, the stack
+    against the same steps written out by hand, and the whole thing replayed from one graph."""
+    import torch.nn.functional as F
+
+    from flash_moe_b200 import FlashMoEConfig, GraphedFlashMoE, check_status
+    from flash_moe_b200.modules.stack import FlashMoEStack
+    from flash_moe_b200.ops.rms_norm import rms_norm
+
+    for dt in (torch.bfloat16, torch.float32):
+        x = (randn((3, 50, 256), 60, dt) * 2.0).cuda()
+        w = (randn((256,), 61, dt) * 0.1 + 1.0).cuda()
+        want = F.rms_norm(x.float(), (256,), w.float(), 1e-6)
+        got = rms_norm(x, w, 1e-6)
+        if dt == torch.float32:
+            torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+        else:
+            assert bf16_ulp_close(got.cpu(), want.to(dt).cpu(), 1).all()
+        assert bf16_ulp_close(rms_norm(x, None).cpu(), F.rms_norm(x.float(), (256,), None, 1e-6).to(dt).cpu(), 1).all() \\
+            if dt == torch.bfloat16 else True
+    stack = FlashMoEStack(FlashMoEConfig(256, 512, "silu", 1024, 8, True), 3, seeds=[0, 1, 2], pre_norm=True)
+    stack = stack.to(torch.bfloat16).eval().cuda()
+    with torch.no_grad():
+        for i, p in enumerate(stack.norms):
+            p.copy_((randn((256,), 70 + i, torch.bfloat16) * 0.1 + 1.0).cuda())
+        x = (randn((2, 200, 256), 62, torch.bfloat16) * 3.0).cuda()
+        cur = x
+        for i, layer in enumerate(stack.layers):
+            cur, _ = layer(rms_norm(cur, stack.norms[i], stack.norm_eps), residual=cur)
+        got, _ = stack(x)
+        g = GraphedFlashMoE(stack, x)
+        replayed = g(x)[0].clone()
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(got, cur) and torch.equal(replayed, got)
+    assert torch.isfinite(got.float()).all()
