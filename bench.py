@@ -545,10 +545,18 @@ def record_c5(dev, peaks, world, rank):
     with torch.no_grad():
         ms = cuda_time(lambda: stack(x), 3, None, warmup=2)
         y, _ = stack(x)
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        finite = bool(torch.isfinite(y.float()).all())
+        # the same stack as a pre-norm decoder block (RMS norm in front of every layer, skip connection un-normalised):
+        # one more kernel per layer, and the activations stay in range
+        stack.norms = torch.nn.ParameterList([torch.nn.Parameter(torch.ones(c["H"], device=dev, dtype=torch.bfloat16))
+                                              for _ in range(c["layers"])])
+        ms_norm = cuda_time(lambda: stack(x), 3, None, warmup=1)
+        y, _ = stack(x)
+        finite_norm = bool(torch.isfinite(y.float()).all())
+    t = torch.tensor([ms, ms_norm], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t)
+    ms, ms_norm = float(t[0]), float(t[1])
     nk = int(math.isqrt(c["N"]))
     Tl = e - s
     flops = c["layers"] * (4.0 * Tl * c["H"] * nk + 6.0 * Tl * c["H"] * c["I"])
@@ -559,7 +567,8 @@ def record_c5(dev, peaks, world, rank):
             "tokens_per_gpu": Tl, "scaling": "strong",
             "roofline": {"bound": "tensor + hbm, summed per stage", "bound_ms": round(bound, 3), "frac": round(bound / ms, 4),
                          "peaks": "sustained bf16 (the pass runs for tens of ms) and copy bandwidth"},
-            "finite_output": bool(torch.isfinite(y.float()).all()),
+            "finite_output": finite,
+            "pre_norm": {"ms": round(ms_norm, 3), "tokens_per_s": c["T"] / (ms_norm * 1e-3), "finite_output": finite_norm},
             "note": "with default init and no normalisation between layers this synthetic stack leaves the bf16 range after "
                     "a few layers; the work done does not depend on it",
             "timing": "CUDA events over whole passes of the stack, max over ranks"}

@@ -1,5 +1,7 @@
 // extern "C" entry points of libfmoe_sm100a.so (declared in include/fmoe.h) and the host-side
 // orchestration of the layer forward.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -21,6 +23,12 @@ int device_sm_count() {
     cache[dev] = n;
   }
   return cache[dev];
+}
+
+// read on every launch (a getenv costs well under a microsecond), so a process can compare both settings
+bool pdl_enabled() {
+  const char* v = std::getenv("FMOE_PDL");
+  return v == nullptr || v[0] != '0';
 }
 
 namespace {

@@ -32,6 +32,47 @@ inline int next_pow2(int v) {
 
 int device_sm_count();  // cached per device (api.cu)
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// The six kernels of a layer forward run back to back on one stream.  Launched with programmatic stream
+// serialisation, a kernel's CTAs may become resident, and run their set-up (barrier init, tensor-map prefetch, tensor
+// memory allocation, index tables), while the previous kernel is still draining; pdl_wait() then blocks until the
+// previous kernel has finished and its writes are visible.  Rules every kernel launched through launch_pdl keeps:
+// all threads call pdl_launch_dependents() first and pdl_wait() before their first access to global memory that is
+// not a launch-time constant (weights are read by kernels only, so even those accesses sit behind the wait).  Because
+// each kernel waits for its predecessor before it finishes, completion is transitive along the stream.
+// FMOE_PDL=0 in the environment turns the attribute off (the device-side instructions are then no-ops).
+bool pdl_enabled();  // api.cu
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// cudaLaunchKernelEx with the programmatic-serialisation attribute (plus a cluster width when cluster_x > 1)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- scalar conversions -------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

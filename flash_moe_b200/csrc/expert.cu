@@ -282,6 +282,8 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
                                                                int world = 1, float* __restrict__ raw_out = nullptr,
                                                                int64_t sharded = 0) {
   extern __shared__ uint4 xs_all[];
+  pdl_launch_dependents();
+  pdl_wait();  // ids and gates come from the kernel before this one
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   // two x-row buffers per warp (xs_stride uint4 each, >= ceil(H/256)*32): while one task is computed, the next
@@ -415,6 +417,8 @@ __global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restric
                                                           int world = 1, int64_t sharded = 0) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int SLOTS = NCH >= 4 ? 4 : 8;
+  pdl_launch_dependents();
+  pdl_wait();  // the weights gs come from the scores pass
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -561,8 +565,9 @@ void launch_accum(const void* up, const int64_t* idx, const float* gs, void* out
   const int64_t want = (tasks + 3) / 4;
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
-  expert_accum_kernel<T, OutT, NCH><<<grid, 128, 0, stream>>>(static_cast<const T*>(up), idx, gs,
-                                                              static_cast<OutT*>(out), T_, H, N, k, colblocks, nullptr, 1);
+  auto kern = expert_accum_kernel<T, OutT, NCH>;
+  (void)launch_pdl(kern, dim3(grid), dim3(128), 0, stream, 1, static_cast<const T*>(up), idx, gs, static_cast<OutT*>(out), T_,
+                   H, N, k, colblocks, nullptr, 1, 0);  // launch errors surface through the caller's launch check
 }
 
 // 16-bit tables are gathered per token (no sort, tensor-core dot products) whatever their size: measured against
@@ -638,10 +643,9 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       const int smem = 4 * 2 * xs_stride * 16;  // two x-row buffers per warp
       auto kern = expert_scores_mma_kernel<T, 4, false, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      kern<<<grid, 128, smem, stream>>>(static_cast<const T*>(rows), static_cast<const T*>(table), idx,
-                                        static_cast<const T*>(gates), out, T_, H, N, k, xs_stride, status, act,
-                                        nullptr, 1, raw_out, 0);
-      FMOE_LAUNCH_CHECK();
+      FMOE_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(128), smem, stream, 1, static_cast<const T*>(rows),
+                               static_cast<const T*>(table), idx, static_cast<const T*>(gates), out, T_, H, N, k, xs_stride,
+                               status, act, nullptr, 1, raw_out, 0));
     }
     return FMOE_OK;
   }

@@ -65,6 +65,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int m_tile = blockIdx.x % num_m_tiles;
   const int n_tile = blockIdx.x / num_m_tiles;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
@@ -81,6 +82,8 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), BLOCK_N);
     ptx::tmem_relinquish();
   }
+  // everything above is independent of earlier kernels; from here on global memory is read
+  pdl_wait();
   // statistics: eval mode straight from the running buffers, training mode from the finalised batch statistics
   for (int c = threadIdx.x; c < num_k_blocks * BLOCK_K; c += kThreads) {
     float m = 0.f, s = 0.f;
@@ -218,10 +221,9 @@ int launch_bn_gemm(const void* x, const void* w, const float* mean, const float*
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int num_m_tiles = static_cast<int>((M + BLOCK_M - 1) / BLOCK_M);
   const int num_n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
-  kern<<<num_m_tiles * num_n_tiles, kThreads, smem, stream>>>(tA, tB, mean, invstd, static_cast<const T*>(rm),
-                                                            static_cast<const T*>(rv), eps, static_cast<T*>(out),
-                                                            static_cast<int>(M), N, K, num_m_tiles, num_k_blocks, status);
-  FMOE_LAUNCH_CHECK();
+  FMOE_CUDA_TRY(launch_pdl(kern, dim3(num_m_tiles * num_n_tiles), dim3(kThreads), smem, stream, 1, tA, tB, mean, invstd,
+                           static_cast<const T*>(rm), static_cast<const T*>(rv), eps, static_cast<T*>(out),
+                           static_cast<int>(M), N, K, num_m_tiles, num_k_blocks, status));
   return FMOE_OK;
 }
 

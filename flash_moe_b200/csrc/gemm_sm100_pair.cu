@@ -55,6 +55,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                          const __grid_constant__ CUtensorMap tmB1, PairEpi ep, int M, int num_m_tiles, int num_n_tiles,
                          int num_k_blocks, int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents();
   const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw_u32);
@@ -98,6 +99,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   ptx::cluster_sync();  // barriers of both CTAs are initialised before anyone signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // barriers, tensor memory and tensor maps are ready; the operands come from the kernel before this one
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -221,20 +223,8 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB0, const CUtensorMap
   const int64_t tiles = static_cast<int64_t>(num_m_tiles) * num_n_tiles;
   const int max_pairs = device_sm_count() / 2;
   const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB0, tB1, ep, static_cast<int>(M), num_m_tiles, num_n_tiles,
-                                   num_k_blocks, status));
+  FMOE_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), SMEM_BYTES, stream, 2, tA, tB0, tB1, ep,
+                           static_cast<int>(M), num_m_tiles, num_n_tiles, num_k_blocks, status));
   return FMOE_OK;
 }
 

@@ -327,6 +327,7 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
   using HK = HalfKey<T>;
   using K = typename HK::type;
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
@@ -359,6 +360,7 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     pq[c] = (static_cast<uint32_t>(lo) << 16) | static_cast<uint32_t>(c - rowstart[lo]);
   }
   __syncthreads();
+  pdl_wait();  // the staircase table above depends on k alone; the logits come from the previous kernel
 
   unsigned char* wbase = smem + L.cta_bytes + warp * L.warp_bytes;
   float* va = reinterpret_cast<float*>(wbase);  // index order
@@ -710,9 +712,8 @@ int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayou
   const int64_t want = (T_ + warps - 1) / warps;
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * per_sm;
   const int grid = static_cast<int>(want < cap ? want : cap);
-  kern<<<grid, warps * 32, smem, stream>>>(static_cast<const T*>(logp), T_, nk, k, L, static_cast<T*>(scores), indices,
-                                           static_cast<T*>(gates), norm);
-  FMOE_LAUNCH_CHECK();
+  FMOE_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, stream, 1, static_cast<const T*>(logp), T_, nk, k, L,
+                           static_cast<T*>(scores), indices, static_cast<T*>(gates), norm));
   return FMOE_OK;
 }
 
