@@ -25,10 +25,12 @@ int device_sm_count() {
   return cache[dev];
 }
 
-// read on every launch (a getenv costs well under a microsecond), so a process can compare both settings
-bool pdl_enabled() {
+// read on every launch (a getenv costs well under a microsecond), so a process can compare settings: FMOE_PDL is a
+// bit mask of kernel classes (see common.cuh) that are launched with programmatic stream serialisation
+bool pdl_enabled(int kernel_class) {
   const char* v = std::getenv("FMOE_PDL");
-  return v == nullptr || v[0] != '0';
+  const int mask = v == nullptr ? kPdlDefaultMask : std::atoi(v);
+  return (mask & kernel_class) != 0;
 }
 
 namespace {

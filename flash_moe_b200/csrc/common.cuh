@@ -40,15 +40,20 @@ int device_sm_count();  // cached per device (api.cu)
 // all threads call pdl_launch_dependents() first and pdl_wait() before their first access to global memory that is
 // not a launch-time constant (weights are read by kernels only, so even those accesses sit behind the wait).  Because
 // each kernel waits for its predecessor before it finishes, completion is transitive along the stream.
-// FMOE_PDL=0 in the environment turns the attribute off (the device-side instructions are then no-ops).
-bool pdl_enabled();  // api.cu
+// FMOE_PDL=<bit mask of kernel classes> in the environment chooses which kernels get the attribute (0: none; the
+// device-side instructions are no-ops without it).
+// measured: the scores pass (4) is slower when it is made resident early - at the benchmark shape 215 vs 213 us per
+// step, at 131072 tokens x 2048 columns 15.4 vs 13.4 ms per layer - so it keeps the plain stream order; the other four
+// together give 211 vs 213 us in a graph and 214 vs 224 us launched eagerly
+constexpr int kPdlDefaultMask = 27;
+bool pdl_enabled(int kernel_class);  // api.cu; classes: 1 router GEMM, 2 top-k, 4 scores, 8 accumulate, 16 MLP GEMMs
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // cudaLaunchKernelEx with the programmatic-serialisation attribute (plus a cluster width when cluster_x > 1)
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
-                              Args&&... args) {
+inline cudaError_t launch_pdl(int kernel_class, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, int cluster_x, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -63,7 +68,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     attr[n].val.clusterDim.z = 1;
     ++n;
   }
-  if (pdl_enabled()) {
+  if (pdl_enabled(kernel_class)) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;

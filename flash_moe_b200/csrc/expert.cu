@@ -282,7 +282,6 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
                                                                int world = 1, float* __restrict__ raw_out = nullptr,
                                                                int64_t sharded = 0) {
   extern __shared__ uint4 xs_all[];
-  pdl_launch_dependents();
   pdl_wait();  // ids and gates come from the kernel before this one
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -320,6 +319,7 @@ __global__ void __launch_bounds__(128) expert_scores_mma_kernel(const T* __restr
     fetch_x(warp_global / groups, xs_buf);
   }
   for (int64_t task = warp_global; task < tasks; task += warps_total) {
+    if (task + warps_total >= tasks) pdl_launch_dependents();  // last task of this warp: the next kernel may set up
     const int64_t t = task / groups;
     const int G = static_cast<int>(task - t * groups);
     const int ja = G * 16 + g, jb = ja + 8;
@@ -417,7 +417,6 @@ __global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restric
                                                           int world = 1, int64_t sharded = 0) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int SLOTS = NCH >= 4 ? 4 : 8;
-  pdl_launch_dependents();
   pdl_wait();  // the weights gs come from the scores pass
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -442,6 +441,7 @@ __global__ void __launch_bounds__(128, 4) expert_accum_kernel(const T* __restric
   float w_next = 0.f;
   if (warp_global < tasks) fetch_slot(warp_global / colblocks, 0, e_next, w_next);
   for (int64_t task = warp_global; task < tasks; task += warps_total) {
+    if (task + warps_total >= tasks) pdl_launch_dependents();  // last task of this warp: the next kernel may set up
     const int64_t t = task / colblocks;
     const int cb = static_cast<int>(task - t * colblocks);
     const int col0 = cb * (32 * VEC * NCH);
@@ -566,7 +566,7 @@ void launch_accum(const void* up, const int64_t* idx, const float* gs, void* out
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   const int grid = static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
   auto kern = expert_accum_kernel<T, OutT, NCH>;
-  (void)launch_pdl(kern, dim3(grid), dim3(128), 0, stream, 1, static_cast<const T*>(up), idx, gs, static_cast<OutT*>(out), T_,
+  (void)launch_pdl(8, kern, dim3(grid), dim3(128), 0, stream, 1, static_cast<const T*>(up), idx, gs, static_cast<OutT*>(out), T_,
                    H, N, k, colblocks, nullptr, 1, 0);  // launch errors surface through the caller's launch check
 }
 
@@ -643,7 +643,7 @@ int run_scores(const void* rows, const void* table, const int64_t* idx, const vo
       const int smem = 4 * 2 * xs_stride * 16;  // two x-row buffers per warp
       auto kern = expert_scores_mma_kernel<T, 4, false, 2>;
       if (smem > 48 * 1024) FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      FMOE_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(128), smem, stream, 1, static_cast<const T*>(rows),
+      FMOE_CUDA_TRY(launch_pdl(4, kern, dim3(grid), dim3(128), smem, stream, 1, static_cast<const T*>(rows),
                                static_cast<const T*>(table), idx, static_cast<const T*>(gates), out, T_, H, N, k, xs_stride,
                                status, act, nullptr, 1, raw_out, 0));
     }

@@ -65,7 +65,6 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int m_tile = blockIdx.x % num_m_tiles;
   const int n_tile = blockIdx.x / num_m_tiles;
 
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
@@ -84,6 +83,15 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
   // everything above is independent of earlier kernels; from here on global memory is read
   pdl_wait();
+  // the first ring of operand tiles is requested before the statistics are fetched, so that the two cold reads overlap
+  int kb_issued = 0;
+  if (threadIdx.x == 0) {
+    for (; kb_issued < kStages && kb_issued < num_k_blocks; ++kb_issued) {
+      ptx::mbar_arrive_expect_tx(full_bar(kb_issued), STAGE_BYTES);
+      ptx::tma_load_2d(a_smem(kb_issued), &tmA, full_bar(kb_issued), kb_issued * BLOCK_K, m_tile * BLOCK_M);
+      ptx::tma_load_2d(b_smem(kb_issued), &tmB, full_bar(kb_issued), kb_issued * BLOCK_K, n_tile * BLOCK_N);
+    }
+  }
   // statistics: eval mode straight from the running buffers, training mode from the finalised batch statistics
   for (int c = threadIdx.x; c < num_k_blocks * BLOCK_K; c += kThreads) {
     float m = 0.f, s = 0.f;
@@ -96,7 +104,10 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         s = invstd[c];
       }
     }
-    stats[c] = make_float2(m, s);
+    // within a k-block the pairs (i, i + 1) of the eight features 8 p .. 8 p + 7 sit at [i / 2][p]: the eight 16-byte reads
+    // a warp makes for one i then cover 128 consecutive bytes instead of one bank group
+    const int fl = c % BLOCK_K;
+    stats[(c - fl) + ((fl & 7) >> 1) * 16 + (fl >> 3) * 2 + (fl & 1)] = make_float2(m, s);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -106,7 +117,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int kb = 0;
+      int kb = kb_issued;
       bool ok = true;
       for (; kb < num_k_blocks; ++kb) {
         const int s = kb % kStages;
@@ -156,7 +167,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       float mm[8], ss[8];
 #pragma unroll
       for (int i = 0; i < 8; i += 2) {
-        const float4 v = *reinterpret_cast<const float4*>(&stats[kb * BLOCK_K + feat0 + i]);
+        const float4 v = *reinterpret_cast<const float4*>(&stats[kb * BLOCK_K + (i >> 1) * 16 + (feat0 >> 3) * 2]);
         mm[i] = v.x; ss[i] = v.y; mm[i + 1] = v.z; ss[i + 1] = v.w;
       }
       uint4* tile = reinterpret_cast<uint4*>(gen + s * STAGE_BYTES);
@@ -221,7 +232,7 @@ int launch_bn_gemm(const void* x, const void* w, const float* mean, const float*
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int num_m_tiles = static_cast<int>((M + BLOCK_M - 1) / BLOCK_M);
   const int num_n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
-  FMOE_CUDA_TRY(launch_pdl(kern, dim3(num_m_tiles * num_n_tiles), dim3(kThreads), smem, stream, 1, tA, tB, mean, invstd,
+  FMOE_CUDA_TRY(launch_pdl(1, kern, dim3(num_m_tiles * num_n_tiles), dim3(kThreads), smem, stream, 1, tA, tB, mean, invstd,
                            static_cast<const T*>(rm), static_cast<const T*>(rv), eps, static_cast<T*>(out),
                            static_cast<int>(M), N, K, num_m_tiles, num_k_blocks, status));
   return FMOE_OK;

@@ -55,7 +55,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                          const __grid_constant__ CUtensorMap tmB1, PairEpi ep, int M, int num_m_tiles, int num_n_tiles,
                          int num_k_blocks, int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
-  pdl_launch_dependents();
   const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw_u32);
@@ -178,6 +177,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ok = __all_sync(kFull, ok);
       if (!ok) break;
       ptx::tc_fence_after();
+      if (tile + npairs >= num_tiles) pdl_launch_dependents();  // last tile: only this epilogue is left
       const uint32_t taddr = tmem_base + acc * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16);
       const int64_t row = static_cast<int64_t>(m_tile) * (2 * BLOCK_M) + rank * BLOCK_M + row_in_tile;
       const bool row_ok = row < M;
@@ -199,6 +199,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   }
 
   // ---------------------------------------------------------------- teardown
+  pdl_launch_dependents();
   __syncwarp();  // the single-lane roles rejoin their warps before the warp-aligned cluster barrier
   ptx::tc_fence_before();
   ptx::cluster_sync();  // nobody frees TMEM or exits while the peer may still signal it
@@ -223,7 +224,7 @@ int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB0, const CUtensorMap
   const int64_t tiles = static_cast<int64_t>(num_m_tiles) * num_n_tiles;
   const int max_pairs = device_sm_count() / 2;
   const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-  FMOE_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kThreads), SMEM_BYTES, stream, 2, tA, tB0, tB1, ep,
+  FMOE_CUDA_TRY(launch_pdl(16, kern, dim3(2 * pairs), dim3(kThreads), SMEM_BYTES, stream, 2, tA, tB0, tB1, ep,
                            static_cast<int>(M), num_m_tiles, num_n_tiles, num_k_blocks, status));
   return FMOE_OK;
 }

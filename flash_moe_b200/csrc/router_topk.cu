@@ -327,7 +327,6 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
   using HK = HalfKey<T>;
   using K = typename HK::type;
   extern __shared__ __align__(16) unsigned char smem[];
-  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
@@ -379,6 +378,7 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
 
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * nwarps + warp; t < ntok;
        t += static_cast<int64_t>(gridDim.x) * nwarps) {
+    if (t + static_cast<int64_t>(gridDim.x) * nwarps >= ntok) pdl_launch_dependents();  // last token of this warp
     // from_logits: the input is the raw router logits [T, 2*nk]; the per-half log-softmax
     // (flash_moe/modules/flash_moe.py:72) is applied here, rounded to T like torch does
     const T* a_row = from_logits ? logp + t * 2 * nk : logp + t * nk;
@@ -712,7 +712,7 @@ int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayou
   const int64_t want = (T_ + warps - 1) / warps;
   const int64_t cap = static_cast<int64_t>(device_sm_count()) * per_sm;
   const int grid = static_cast<int>(want < cap ? want : cap);
-  FMOE_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(warps * 32), smem, stream, 1, static_cast<const T*>(logp), T_, nk, k, L,
+  FMOE_CUDA_TRY(launch_pdl(2, kern, dim3(grid), dim3(warps * 32), smem, stream, 1, static_cast<const T*>(logp), T_, nk, k, L,
                            static_cast<T*>(scores), indices, static_cast<T*>(gates), norm));
   return FMOE_OK;
 }
