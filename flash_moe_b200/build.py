@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-O3", "-std=c++17", "-lineinfo",
         "--shared", "-Xcompiler", "-fPIC",
         "--threads", "0",
-        "-o", LIB_PATH,
+        "-o", LIB_PATH + ".tmp",
     ] + _sources()
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
@@ -52,6 +52,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(LIB_PATH + ".tmp", LIB_PATH)  # readers see the old library or the new one, never a partial file
     if verbose:
         print(res.stdout + res.stderr)
     return LIB_PATH

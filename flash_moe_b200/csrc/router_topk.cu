@@ -274,7 +274,10 @@ __device__ __forceinline__ uint64_t shfl_xor_key(uint64_t v, int m) {
   return static_cast<uint64_t>(__shfl_xor_sync(kFull, static_cast<unsigned long long>(v), m));
 }
 
-// Descending bitonic sort of 32*E keys held as element i = r*32 + lane in a[r].
+// Descending bitonic sort of 32*E keys in the lane-blocked layout: element i = lane * E + r sits in a[r].  Strides
+// below E exchange two registers of one lane (no shuffle: 15 shuffle stages for any E >= 1 instead of up to 35 with
+// the keys dealt round-robin over the lanes); the direction of a block folds into the comparison predicate, so an
+// exchange costs one compare and two selects per pair and a shuffle stage one shuffle, one compare and one select per key.
 template <int E, typename K>
 __device__ __forceinline__ void bitonic_desc_regs(K (&a)[E], int lane) {
   constexpr int n = 32 * E;
@@ -282,30 +285,89 @@ __device__ __forceinline__ void bitonic_desc_regs(K (&a)[E], int lane) {
   for (int size = 2; size <= n; size <<= 1) {
 #pragma unroll
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      if (stride >= 32) {
-        const int rs = stride >> 5;
+      if (stride >= E) {
+        const int ls = stride / E;
+        const bool desc = (size == n) || (((lane * E) & size) == 0);  // size >= 2 E here: decided by the lane
+        const bool keep_max = ((lane & ls) == 0) == desc;
 #pragma unroll
         for (int r = 0; r < E; ++r) {
-          if ((r & rs) == 0) {
-            const bool desc = (((r << 5) & size) == 0);  // size >= 64 here: decided by r alone
-            const K x = a[r], y = a[r | rs];
-            const K hi = x > y ? x : y, lo = x > y ? y : x;
-            a[r] = desc ? hi : lo;
-            a[r | rs] = desc ? lo : hi;
-          }
+          const K other = shfl_xor_key(a[r], ls);
+          a[r] = ((other > a[r]) == keep_max) ? other : a[r];
         }
       } else {
 #pragma unroll
         for (int r = 0; r < E; ++r) {
-          const K other = shfl_xor_key(a[r], stride);
-          const int i = (r << 5) | lane;
-          const bool desc = ((i & size) == 0);
-          const bool lower = ((lane & stride) == 0);
-          const K hi = a[r] > other ? a[r] : other, lo = a[r] > other ? other : a[r];
-          a[r] = (lower == desc) ? hi : lo;
+          if ((r & stride) == 0) {
+            const bool desc = (size == n) || (size < E ? ((r & size) == 0) : (((lane * E) & size) == 0));
+            const K x = a[r], y = a[r | stride];
+            const bool sw = (x < y) == desc;
+            a[r] = sw ? y : x;
+            a[r | stride] = sw ? x : y;
+          }
         }
       }
     }
+  }
+}
+
+// One lane's E consecutive elements of a row (element lane * E + r -> v[r]); entries past nk read as -inf.  Whole
+// rows of 32 E elements at a 16-byte aligned address are fetched with one or a few vector loads.
+template <typename T, int E>
+__device__ __forceinline__ void load_blocked(const T* __restrict__ row, int nk, int lane, float (&v)[E]) {
+  constexpr int BYTES = E * static_cast<int>(sizeof(T));
+  if (BYTES >= 4 && nk == 32 * E && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+    __align__(16) T tmp[E];
+    const T* src = row + lane * E;
+    if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+      for (int j = 0; j < BYTES / 16; ++j) reinterpret_cast<uint4*>(tmp)[j] = reinterpret_cast<const uint4*>(src)[j];
+    } else if constexpr (BYTES == 8) {
+      *reinterpret_cast<uint2*>(tmp) = *reinterpret_cast<const uint2*>(src);
+    } else if constexpr (BYTES == 4) {
+      *reinterpret_cast<uint32_t*>(tmp) = *reinterpret_cast<const uint32_t*>(src);
+    }
+#pragma unroll
+    for (int r = 0; r < E; ++r) v[r] = to_f32<T>(tmp[r]);
+  } else {
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int i = lane * E + r;
+      v[r] = (i < nk) ? to_f32<T>(row[i]) : -INFINITY;
+    }
+  }
+}
+
+// One lane's E consecutive entries of a per-warp shared-memory array (16-byte aligned base, 32 E entries)
+template <int E>
+__device__ __forceinline__ void store_blocked(float* base, int lane, const float (&v)[E]) {
+  float* dst = base + lane * E;
+  if constexpr (E % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < E / 4; ++j)
+      reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+  } else {
+#pragma unroll
+    for (int r = 0; r < E; ++r) dst[r] = v[r];
+  }
+}
+template <int E>
+__device__ __forceinline__ void store_blocked(uint16_t* base, int lane, const uint32_t (&v)[E]) {  // v[r] < 65536
+  uint16_t* dst = base + lane * E;
+  if constexpr (E % 8 == 0) {
+#pragma unroll
+    for (int j = 0; j < E / 8; ++j)
+      reinterpret_cast<uint4*>(dst)[j] =
+          make_uint4(v[8 * j] | (v[8 * j + 1] << 16), v[8 * j + 2] | (v[8 * j + 3] << 16),
+                     v[8 * j + 4] | (v[8 * j + 5] << 16), v[8 * j + 6] | (v[8 * j + 7] << 16));
+  } else if constexpr (E == 4) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<uint32_t*>(dst) = v[0] | (v[1] << 16);
+  } else {
+#pragma unroll
+    for (int r = 0; r < E; ++r) dst[r] = static_cast<uint16_t>(v[r]);
   }
 }
 
@@ -386,12 +448,8 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     // 1. load, keep the index-order copy, sort both halves in registers
     K ka[E], kb[E];
     float la[E], lb[E];
-#pragma unroll
-    for (int r = 0; r < E; ++r) {
-      const int i = (r << 5) | lane;
-      la[r] = (i < nk) ? to_f32<T>(a_row[i]) : -INFINITY;
-      lb[r] = (i < nk) ? to_f32<T>(b_row[i]) : -INFINITY;
-    }
+    load_blocked<T, E>(a_row, nk, lane, la);  // lane-blocked: element lane * E + r
+    load_blocked<T, E>(b_row, nk, lane, lb);
     if (from_logits) {
       float ma = -INFINITY, mb = -INFINITY;
 #pragma unroll
@@ -404,7 +462,7 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       float sa_ = 0.f, sb_ = 0.f;
 #pragma unroll
       for (int r = 0; r < E; ++r) {
-        const int i = (r << 5) | lane;
+        const int i = lane * E + r;
         if (i < nk) { sa_ += expf(la[r] - ma); sb_ += expf(lb[r] - mb); }
       }
 #pragma unroll
@@ -421,28 +479,29 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     }
 #pragma unroll
     for (int r = 0; r < E; ++r) {
-      const int i = (r << 5) | lane;
-      if (i < nk) {
-        const float a = la[r] + 0.0f;
-        const float b = lb[r] + 0.0f;
-        va[i] = a;
-        vb[i] = b;
-        ka[r] = HK::make(a, i);
-        kb[r] = HK::make(b, i);
-      } else {
-        ka[r] = 0;
-        kb[r] = 0;
-      }
+      const int i = lane * E + r;
+      la[r] += 0.0f;  // -0 -> +0
+      lb[r] += 0.0f;
+      ka[r] = (i < nk) ? HK::make(la[r], i) : K(0);
+      kb[r] = (i < nk) ? HK::make(lb[r], i) : K(0);
     }
+    store_blocked<E>(va, lane, la);  // index order (entries past nk are never read)
+    store_blocked<E>(vb, lane, lb);
     bitonic_desc_regs<E, K>(ka, lane);
     bitonic_desc_regs<E, K>(kb, lane);
+    {
+      uint32_t ida[E], idb[E];
 #pragma unroll
-    for (int r = 0; r < E; ++r) {
-      const int i = (r << 5) | lane;
-      sa[i] = HK::value(ka[r]);
-      sb[i] = HK::value(kb[r]);
-      ia[i] = static_cast<uint16_t>(HK::id(ka[r]));
-      ib[i] = static_cast<uint16_t>(HK::id(kb[r]));
+      for (int r = 0; r < E; ++r) {
+        la[r] = HK::value(ka[r]);
+        lb[r] = HK::value(kb[r]);
+        ida[r] = HK::id(ka[r]) & 0xFFFFu;
+        idb[r] = HK::id(kb[r]) & 0xFFFFu;
+      }
+      store_blocked<E>(sa, lane, la);  // rank order
+      store_blocked<E>(sb, lane, lb);
+      store_blocked<E>(ia, lane, ida);
+      store_blocked<E>(ib, lane, idb);
     }
     __syncwarp();
 
@@ -623,7 +682,7 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       uint32_t w[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const uint64_t key = win[r * 32 + lane];
+        const uint64_t key = win[lane * 2 + r];
         w[r] = key == 0 ? 0u : static_cast<uint32_t>(HalfKey<T>::make(key_val(key), key_id(key)));
       }
       bitonic_desc_regs<2, uint32_t>(w, lane);
@@ -631,20 +690,20 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       for (int r = 0; r < 2; ++r) {
         const uint32_t key32 = w[r];
         const float sc = static_cast<float>(HalfKey<T>::value(static_cast<typename HalfKey<T>::type>(key32)));
-        win[r * 32 + lane] = make_key(f32_to_ord(sc + 0.0f), HalfKey<T>::id(static_cast<typename HalfKey<T>::type>(key32)));
+        win[lane * 2 + r] = make_key(f32_to_ord(sc + 0.0f), HalfKey<T>::id(static_cast<typename HalfKey<T>::type>(key32)));
       }
     } else if (kp <= 32) {
       uint64_t w[1] = {lane < kp ? win[lane] : 0};
       bitonic_desc_regs<1, uint64_t>(w, lane);
       if (lane < kp) win[lane] = w[0];
     } else if (kp == 64) {
-      uint64_t w[2] = {win[lane], win[32 + lane]};
+      uint64_t w[2] = {win[2 * lane], win[2 * lane + 1]};
       bitonic_desc_regs<2, uint64_t>(w, lane);
-      win[lane] = w[0]; win[32 + lane] = w[1];
+      win[2 * lane] = w[0]; win[2 * lane + 1] = w[1];
     } else if (kp == 128) {
-      uint64_t w[4] = {win[lane], win[32 + lane], win[64 + lane], win[96 + lane]};
+      uint64_t w[4] = {win[4 * lane], win[4 * lane + 1], win[4 * lane + 2], win[4 * lane + 3]};
       bitonic_desc_regs<4, uint64_t>(w, lane);
-      win[lane] = w[0]; win[32 + lane] = w[1]; win[64 + lane] = w[2]; win[96 + lane] = w[3];
+      win[4 * lane] = w[0]; win[4 * lane + 1] = w[1]; win[4 * lane + 2] = w[2]; win[4 * lane + 3] = w[3];
     } else {
       bitonic_desc(win, nullptr, kp, lane);
     }
