@@ -379,7 +379,9 @@ struct RouterRegLayout {
   int nkp, kp, kq, C, Cp;
 };
 
-template <typename T, int E>
+// CPL > 0: the staircase candidates (at most 32 * CPL of them) stay in registers, CPL per lane, through the threshold
+// search and the emit step, whose loops then have compile-time bounds and no shared-memory round trips between rounds.
+template <typename T, int E, int CPL = 0>
 __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restrict__ logp, int64_t ntok, int nk, int k,
                                                              RouterRegLayout L, T* __restrict__ scores,
                                                              int64_t* __restrict__ indices, T* __restrict__ gates,
@@ -507,11 +509,28 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
 
     // 2. staircase candidate scores; track the smallest to narrow the threshold search
     uint32_t cmin = 0xFFFFFFFFu;
-    for (int c = lane; c < C; c += 32) {
-      const uint32_t e = pq[c];
-      const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(sa[e >> 16], sb[e & 0xFFFFu])) + 0.0f);
-      cs[c] = o;
-      cmin = min(cmin, o);
+    uint32_t csr[CPL > 0 ? CPL : 1], pqr[CPL > 0 ? CPL : 1];
+    if constexpr (CPL > 0) {
+#pragma unroll
+      for (int j = 0; j < CPL; ++j) {
+        const int c = 32 * j + lane;
+        const bool in = c < C;
+        const uint32_t e = in ? pq[c] : 0u;
+        const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(sa[e >> 16], sb[e & 0xFFFFu])) + 0.0f);
+        pqr[j] = e;
+        csr[j] = in ? o : 0u;  // 0 is below the key of every float, -inf included
+        if (in) {
+          cs[c] = o;  // the tie search below looks up single cells
+          cmin = min(cmin, o);
+        }
+      }
+    } else {
+      for (int c = lane; c < C; c += 32) {
+        const uint32_t e = pq[c];
+        const uint32_t o = f32_to_ord(round_to<T>(__fadd_rn(sa[e >> 16], sb[e & 0xFFFFu])) + 0.0f);
+        cs[c] = o;
+        cmin = min(cmin, o);
+      }
     }
     cmin = __reduce_min_sync(kFull, cmin);
     __syncwarp();
@@ -525,7 +544,12 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       for (int bit = top; bit >= LOW; --bit) {
         const uint32_t trial = tau | (1u << bit);
         int n_ge = 0;
-        for (int c = lane; c < C; c += 32) n_ge += (cs[c] >= trial) ? 1 : 0;
+        if constexpr (CPL > 0) {
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) n_ge += (csr[j] >= trial) ? 1 : 0;
+        } else {
+          for (int c = lane; c < C; c += 32) n_ge += (cs[c] >= trial) ? 1 : 0;
+        }
         n_ge = __reduce_add_sync(kFull, n_ge);
         if (n_ge >= k) tau = trial;
       }
@@ -534,15 +558,13 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
 
     // emit everything above tau; collect the staircase candidates equal to tau in the tie list
     int filled = 0, nties = 0;
-    for (int base = 0; base < C; base += 32) {
-      const int c = base + lane;
-      const uint32_t v = (c < C) ? cs[c] : 0u;
+    auto emit = [&](int c, uint32_t v, uint32_t e, bool known) {
       const bool g = (c < C) && (v > tau);
       const bool eq = (c < C) && (v == tau);
       const unsigned bal = __ballot_sync(kFull, g);
       const unsigned beq = __ballot_sync(kFull, eq);
       if (g || eq) {
-        const uint32_t e = pq[c];
+        if (!known) e = pq[c];
         const uint32_t flat = static_cast<uint32_t>(ia[e >> 16]) * static_cast<uint32_t>(nk) + ib[e & 0xFFFFu];
         if (g) {
           const int pos = filled + __popc(bal & ((1u << lane) - 1u));
@@ -554,6 +576,16 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
       }
       filled += __popc(bal);
       nties += __popc(beq);
+    };
+    if constexpr (CPL > 0) {
+#pragma unroll
+      for (int j = 0; j < CPL; ++j)
+        if (32 * j < C) emit(32 * j + lane, csr[j], pqr[j], true);
+    } else {
+      for (int base = 0; base < C; base += 32) {
+        const int c = base + lane;
+        emit(c, (c < C) ? cs[c] : 0u, 0u, false);
+      }
     }
     int need = k - filled;
 
@@ -566,8 +598,9 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     if (lane == 0) *tcnt = nties;
     __syncwarp();
     for (int p = lane; p < kq; p += 32) {
-      const int len = min(k / (p + 1), kq);
-      if (len < nk && cs[rowstart[p] + len - 1] >= tau) {
+      const int rs = rowstart[p];
+      const int len = ((p + 1 < kq) ? rowstart[p + 1] : C) - rs;  // = min(k / (p + 1), kq) without the division
+      if (len < nk && cs[rs + len - 1] >= tau) {
         const float a = sa[p];
         const uint32_t ida = static_cast<uint32_t>(ia[p]) * static_cast<uint32_t>(nk);
         for (int q = len; q < nk; ++q) {
@@ -598,7 +631,15 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     nties = *tcnt;
     __syncwarp();
     const bool tie_list_ok = nties <= kTieCap;
-    if (tie_list_ok && need > 0) {
+    if (tie_list_ok && need > 0 && nties <= 32) {
+      // the usual case, a handful of ties: one id per lane, its rank among them by a round of shuffles
+      const uint32_t id = lane < nties ? tl[lane] : 0xFFFFFFFFu;
+      int rank = 0;
+      for (int j = 0; j < nties; ++j) rank += (__shfl_sync(kFull, id, j) < id) ? 1 : 0;
+      if (lane < nties && rank < need) win[filled + rank] = make_key(tau, id);
+      filled += min(nties, need);
+      need = k - filled;
+    } else if (tie_list_ok && need > 0) {
       uint32_t phi = 0xFFFFFFFFu;  // ids <= phi are taken
       if (nties > need) {
         // phi = the need-th smallest id = the largest v with fewer than `need` ids below v
@@ -759,11 +800,11 @@ RouterRegLayout make_reg_layout(int nk, int k) {
   return L;
 }
 
-template <typename T, int E>
-int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayout& L, int warps, void* scores,
-               int64_t* indices, void* gates, int norm, cudaStream_t stream) {
+template <typename T, int E, int CPL = 0>
+int launch_reg_cpl(const void* logp, int64_t T_, int nk, int k, const RouterRegLayout& L, int warps, void* scores,
+                   int64_t* indices, void* gates, int norm, cudaStream_t stream) {
   const int smem = L.cta_bytes + warps * L.warp_bytes;
-  auto kern = router_topk_reg_kernel<T, E>;
+  auto kern = router_topk_reg_kernel<T, E, CPL>;
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int per_sm = 1;
   FMOE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, smem));
@@ -774,6 +815,19 @@ int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayou
   FMOE_CUDA_TRY(launch_pdl(2, kern, dim3(grid), dim3(warps * 32), smem, stream, 1, static_cast<const T*>(logp), T_, nk, k, L,
                            static_cast<T*>(scores), indices, static_cast<T*>(gates), norm));
   return FMOE_OK;
+}
+
+// 16-bit dtypes with at least 128 keys per half (the shapes of real layers) keep the candidates in registers when
+// there are at most 32 * 22 of them (top-k up to 128); other shapes walk them in shared memory
+template <typename T, int E>
+int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayout& L, int warps, void* scores,
+               int64_t* indices, void* gates, int norm, cudaStream_t stream) {
+  if constexpr (sizeof(T) == 2 && E >= 4) {
+    if (L.C <= 32 * 4) return launch_reg_cpl<T, E, 4>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+    if (L.C <= 32 * 10) return launch_reg_cpl<T, E, 10>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+    if (L.C <= 32 * 22) return launch_reg_cpl<T, E, 22>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
+  }
+  return launch_reg_cpl<T, E, 0>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
 }
 
 // register kernel when the halves fit 32 keys per lane and the per-warp scratch stays small
