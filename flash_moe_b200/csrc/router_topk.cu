@@ -18,6 +18,8 @@
 //      gates = exp(score) (and the row renormalisation of flash_moe/modules/flash_moe.py:80-85).
 //
 // One warp owns one token; all scratch lives in shared memory.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -447,63 +449,56 @@ __global__ void __launch_bounds__(256) router_topk_reg_kernel(const T* __restric
     // (flash_moe/modules/flash_moe.py:72) is applied here, rounded to T like torch does
     const T* a_row = from_logits ? logp + t * 2 * nk : logp + t * nk;
     const T* b_row = from_logits ? a_row + nk : logp + (ntok + t) * nk;
-    // 1. load, keep the index-order copy, sort both halves in registers
-    K ka[E], kb[E];
-    float la[E], lb[E];
-    load_blocked<T, E>(a_row, nk, lane, la);  // lane-blocked: element lane * E + r
-    load_blocked<T, E>(b_row, nk, lane, lb);
-    if (from_logits) {
-      float ma = -INFINITY, mb = -INFINITY;
+    // 1. per half: load (lane-blocked: element lane * E + r in register r), optional log-softmax, keep the
+    //    index-order copy, sort in registers, store the rank-order values and ids.  The two halves run through ONE copy
+    //    of this code (the loop is not unrolled): the unrolled sorting network is most of the kernel's instructions -
+    //    at 16 keys per lane two copies alone exceed 70 KB - and only one half's keys are live at a time.
+    //    Measured, 16384 tokens x 512 keys top-128 | 16384 x 1024 top-16 | 131072 x 256 top-32 | 4096 x 128 top-64 (us):
+    //    this form 330 | 532 | 559 | 21.5; both halves unrolled side by side 348 | 663 | 539 | 22.5; keys dealt round-robin
+    //    over the lanes (r * 32 + lane, 25-35 shuffle stages) unrolled side by side 304 | 584 | 803 | 25.6, in one copy
+    //    476 | 962 - with 16 or 32 keys per lane few warps are resident and the two halves' independent chains hide
+    //    each other's latency, which the single copy gives up and the smaller code buys back.
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      const T* row = h == 0 ? a_row : b_row;
+      float* vh = h == 0 ? va : vb;
+      float* sh = h == 0 ? sa : sb;
+      uint16_t* ih = h == 0 ? ia : ib;
+      K key[E];
+      float lv[E];
+      load_blocked<T, E>(row, nk, lane, lv);
+      if (from_logits) {
+        float m = -INFINITY;
 #pragma unroll
-      for (int r = 0; r < E; ++r) { ma = fmaxf(ma, la[r]); mb = fmaxf(mb, lb[r]); }
+        for (int r = 0; r < E; ++r) m = fmaxf(m, lv[r]);
 #pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        ma = fmaxf(ma, __shfl_xor_sync(kFull, ma, d));
-        mb = fmaxf(mb, __shfl_xor_sync(kFull, mb, d));
+        for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, d));
+        float sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < E; ++r)
+          if (lane * E + r < nk) sum += expf(lv[r] - m);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(kFull, sum, d);
+        const float lg = logf(sum);
+#pragma unroll
+        for (int r = 0; r < E; ++r) lv[r] = round_to<T>((lv[r] - m) - lg);
       }
-      float sa_ = 0.f, sb_ = 0.f;
 #pragma unroll
       for (int r = 0; r < E; ++r) {
         const int i = lane * E + r;
-        if (i < nk) { sa_ += expf(la[r] - ma); sb_ += expf(lb[r] - mb); }
+        lv[r] += 0.0f;  // -0 -> +0
+        key[r] = (i < nk) ? HK::make(lv[r], i) : K(0);
       }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        sa_ += __shfl_xor_sync(kFull, sa_, d);
-        sb_ += __shfl_xor_sync(kFull, sb_, d);
-      }
-      const float lga = logf(sa_), lgb = logf(sb_);
+      store_blocked<E>(vh, lane, lv);  // index order (entries past nk are never read)
+      bitonic_desc_regs<E, K>(key, lane);
+      uint32_t idr[E];
 #pragma unroll
       for (int r = 0; r < E; ++r) {
-        la[r] = round_to<T>((la[r] - ma) - lga);
-        lb[r] = round_to<T>((lb[r] - mb) - lgb);
+        lv[r] = HK::value(key[r]);
+        idr[r] = HK::id(key[r]) & 0xFFFFu;
       }
-    }
-#pragma unroll
-    for (int r = 0; r < E; ++r) {
-      const int i = lane * E + r;
-      la[r] += 0.0f;  // -0 -> +0
-      lb[r] += 0.0f;
-      ka[r] = (i < nk) ? HK::make(la[r], i) : K(0);
-      kb[r] = (i < nk) ? HK::make(lb[r], i) : K(0);
-    }
-    store_blocked<E>(va, lane, la);  // index order (entries past nk are never read)
-    store_blocked<E>(vb, lane, lb);
-    bitonic_desc_regs<E, K>(ka, lane);
-    bitonic_desc_regs<E, K>(kb, lane);
-    {
-      uint32_t ida[E], idb[E];
-#pragma unroll
-      for (int r = 0; r < E; ++r) {
-        la[r] = HK::value(ka[r]);
-        lb[r] = HK::value(kb[r]);
-        ida[r] = HK::id(ka[r]) & 0xFFFFu;
-        idb[r] = HK::id(kb[r]) & 0xFFFFu;
-      }
-      store_blocked<E>(sa, lane, la);  // rank order
-      store_blocked<E>(sb, lane, lb);
-      store_blocked<E>(ia, lane, ida);
-      store_blocked<E>(ib, lane, idb);
+      store_blocked<E>(sh, lane, lv);  // rank order
+      store_blocked<E>(ih, lane, idr);
     }
     __syncwarp();
 
@@ -818,14 +813,17 @@ int launch_reg_cpl(const void* logp, int64_t T_, int nk, int k, const RouterRegL
 }
 
 // 16-bit dtypes with at least 128 keys per half (the shapes of real layers) keep the candidates in registers when
-// there are at most 32 * 22 of them (top-k up to 128); other shapes walk them in shared memory
+// there are at most 320 of them (top-k up to 64: 22.5 vs 23.4 us at 4096 tokens x 128 keys, 539 vs 629 us at
+// 131072 x 256 keys, top-32); with 22 per lane (top-128) the shared-memory walk measured faster (348 vs 382 us)
 template <typename T, int E>
 int launch_reg(const void* logp, int64_t T_, int nk, int k, const RouterRegLayout& L, int warps, void* scores,
                int64_t* indices, void* gates, int norm, cudaStream_t stream) {
+  const char* force = std::getenv("FMOE_TOPK_CANDIDATES");  // measurement aid: "smem" forces the shared-memory walk
+  const bool in_regs = force == nullptr || force[0] != 's';
   if constexpr (sizeof(T) == 2 && E >= 4) {
+    if (!in_regs) return launch_reg_cpl<T, E, 0>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
     if (L.C <= 32 * 4) return launch_reg_cpl<T, E, 4>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
     if (L.C <= 32 * 10) return launch_reg_cpl<T, E, 10>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
-    if (L.C <= 32 * 22) return launch_reg_cpl<T, E, 22>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
   }
   return launch_reg_cpl<T, E, 0>(logp, T_, nk, k, L, warps, scores, indices, gates, norm, stream);
 }
