@@ -152,6 +152,33 @@ def test_cuda_graph_replay_matches_eager():
     assert torch.equal(y3, want3)
 
 
+def test_launch_and_candidate_switches_do_not_change_results(monkeypatch):
+    """Programmatic dependent launch only changes when a kernel may start, and the top-k's register-resident
+    candidate list only where the candidates live: the layer's outputs are bit-equal with either switched off, at a
+    small shape and at the benchmark's (the one that uses the 10-per-lane candidate registers)."""
+    from flash_moe_b200 import check_status
+
+    for (H, I, N, k, shape) in ((256, 512, 1024, 8, (2, 96, 256)), (1024, 4096, 16384, 64, (1, 1024, 1024))):
+        _, ours = make_layer_pair(H, I, N, k, False, torch.bfloat16)
+        ours.eval()
+        x = randn(shape, 4, torch.bfloat16).cuda()
+        with torch.no_grad():
+            monkeypatch.delenv("FMOE_PDL", raising=False)
+            monkeypatch.delenv("FMOE_TOPK_CANDIDATES", raising=False)
+            y, logits = ours(x)
+            monkeypatch.setenv("FMOE_PDL", "0")
+            y_plain, logits_plain = ours(x)
+            monkeypatch.setenv("FMOE_PDL", "31")
+            y_all, _ = ours(x)
+            monkeypatch.delenv("FMOE_PDL")
+            monkeypatch.setenv("FMOE_TOPK_CANDIDATES", "smem")
+            y_smem, _ = ours(x)
+        torch.cuda.synchronize()
+        check_status()
+        assert torch.equal(y, y_plain) and torch.equal(logits, logits_plain)
+        assert torch.equal(y, y_all) and torch.equal(y, y_smem)
+
+
 def test_stage_events_cover_the_forward():
     """The library records an event pair per stage (enum fmoe_stage); the stages follow one another on the stream."""
     from flash_moe_b200 import StageTimer, _lib
