@@ -48,8 +48,11 @@ def test_router_topk_matches_reference_kernel_fixture(golden_dir, name):
     assert np.array_equal(got_i.numpy(), z["indices"])
 
 
-def test_router_heavy_ties_and_infinities():
-    T, nk, k = 16, 64, 32
+@pytest.mark.parametrize("T,nk,k", [(16, 64, 32), (8, 128, 64), (8, 256, 32), (6, 512, 16)])
+def test_router_heavy_ties_and_infinities(T, nk, k):
+    """Log-probabilities on a grid of 0.5: hundreds of candidates tie with the threshold (short tie lists ranked by
+    shuffles, long ones by the bitwise search, overflowing ones by the per-row search), at shapes that keep the
+    candidates in shared memory (64 keys) and in registers (128 and more keys)."""
     lp = torch.round(randn((2, T, nk), 3) * 2) / 2 - 3.0
     lp[0, 0, :] = -1.0  # a whole half tied
     lp[1, 1, :] = float("-inf")  # every sum is -inf for this token
