@@ -12,6 +12,8 @@
 //   warps 2..5         epilogue: tcgen05.ld the accumulator (one row per thread), round, store.
 // Columns of x beyond K arrive as zeros from TMA and are normalised with mean 0 / scale 0, so they stay zero.
 // Every wait is bounded; a wait that runs out raises FMOE_STATUS_WAIT_TIMEOUT and the CTA drains and leaves.
+#include <cstdlib>
+
 #include "gemm_epilogue.cuh"
 
 namespace fmoe {
@@ -27,8 +29,11 @@ using epi::UmmaFmt;
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// ring depth: 32 KB stages for 128-column tiles, 48 KB stages for 256-column tiles
-template <int BLOCK_N> struct RingDepth { static constexpr int v = BLOCK_N <= 128 ? 6 : 4; };
+// ring depth: 6 x 24 KB or 6 x 32 KB stages for 128-column tiles, 4 x 48 KB for 256-column tiles.  Deeper does not
+// help (8 stages measured the same): timestamps taken inside the kernel show the tiles landed and normalised well ahead
+// of the MMA thread, which needs about 700 cycles per k-block (four tcgen05.mma of K = 16 and a commit) whether the
+// tile has 64 or 128 rows - the issue pace of the MMAs, not the operand feed, sets the length of the main loop here.
+template <int BLOCK_M, int BLOCK_N> struct RingDepth { static constexpr int v = BLOCK_N <= 128 ? 6 : 4; };
 
 // BLOCK_M = 128, or 64 for small problems (twice the CTAs, half the x tile to fetch and normalise per CTA).  With
 // M = 64 the accumulator's row i sits in TMEM lane 32 * (i / 16) + i % 16: each of the four epilogue warps finds 16
@@ -42,8 +47,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int kStages = RingDepth<BLOCK_N>::v;
-  constexpr int kPieces = BLOCK_M * 8 / 256;  // 16-byte pieces of the x tile per normalising thread
+  constexpr int kStages = RingDepth<BLOCK_M, BLOCK_N>::v;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -68,7 +72,7 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(ready_bar(s), kXformWarps);
+      ptx::mbar_init(ready_bar(s), kXformWarps / 2);  // one group of four warps normalises a k-block
       ptx::mbar_init(empty_bar(s), 1);
     }
     ptx::mbar_init(tfull_bar, 1);
@@ -92,22 +96,51 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       ptx::tma_load_2d(b_smem(kb_issued), &tmB, full_bar(kb_issued), kb_issued * BLOCK_K, n_tile * BLOCK_N);
     }
   }
-  // statistics: eval mode straight from the running buffers, training mode from the finalised batch statistics
-  for (int c = threadIdx.x; c < num_k_blocks * BLOCK_K; c += kThreads) {
-    float m = 0.f, s = 0.f;
-    if (c < K) {
+  // statistics: eval mode straight from the running buffers, training mode from the finalised batch statistics.
+  // One thread fetches the eight features 8 p .. 8 p + 7 of a k-block with vector loads (all of a thread's loads are in
+  // flight together: the buffers are cold, and fetching them one feature at a time took four DRAM round trips), and
+  // writes them as four 16-byte entries: within a k-block the pairs (i, i + 1) of those eight features sit at
+  // [i / 2][p], so the eight 16-byte reads a warp makes for one i cover 128 consecutive bytes instead of one bank group.
+  const bool vec_stats = (running_mean != nullptr)
+                             ? (sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(running_mean) | reinterpret_cast<uintptr_t>(running_var)) & 15u) == 0)
+                             : (((reinterpret_cast<uintptr_t>(mean) | reinterpret_cast<uintptr_t>(invstd)) & 15u) == 0);
+  for (int ch = threadIdx.x; ch < num_k_blocks * (BLOCK_K / 8); ch += kThreads) {
+    const int c0 = ch * 8;
+    float m[8], sd[8];
+    if (vec_stats && c0 + 8 <= K) {
       if (running_mean != nullptr) {
-        m = to_f32<T>(running_mean[c]);
-        s = 1.0f / sqrtf(to_f32<T>(running_var[c]) + eps);
+        float v[8];
+        unpack16<T>(ldg16(running_mean + c0), m);
+        unpack16<T>(ldg16(running_var + c0), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sd[i] = 1.0f / sqrtf(v[i] + eps);
       } else {
-        m = mean[c];
-        s = invstd[c];
+        const float4 m0 = *reinterpret_cast<const float4*>(mean + c0), m1 = *reinterpret_cast<const float4*>(mean + c0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(invstd + c0), s1 = *reinterpret_cast<const float4*>(invstd + c0 + 4);
+        m[0] = m0.x; m[1] = m0.y; m[2] = m0.z; m[3] = m0.w; m[4] = m1.x; m[5] = m1.y; m[6] = m1.z; m[7] = m1.w;
+        sd[0] = s0.x; sd[1] = s0.y; sd[2] = s0.z; sd[3] = s0.w; sd[4] = s1.x; sd[5] = s1.y; sd[6] = s1.z; sd[7] = s1.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i;
+        m[i] = 0.f;
+        sd[i] = 0.f;
+        if (c < K) {
+          if (running_mean != nullptr) {
+            m[i] = to_f32<T>(running_mean[c]);
+            sd[i] = 1.0f / sqrtf(to_f32<T>(running_var[c]) + eps);
+          } else {
+            m[i] = mean[c];
+            sd[i] = invstd[c];
+          }
+        }
       }
     }
-    // within a k-block the pairs (i, i + 1) of the eight features 8 p .. 8 p + 7 sit at [i / 2][p]: the eight 16-byte reads
-    // a warp makes for one i then cover 128 consecutive bytes instead of one bank group
-    const int fl = c % BLOCK_K;
-    stats[(c - fl) + ((fl & 7) >> 1) * 16 + (fl >> 3) * 2 + (fl & 1)] = make_float2(m, s);
+    const int kb0 = (c0 / BLOCK_K) * BLOCK_K, pp = (c0 % BLOCK_K) >> 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<float4*>(&stats[kb0 + j * 16 + pp * 2]) = make_float4(m[2 * j], sd[2 * j], m[2 * j + 1], sd[2 * j + 1]);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -155,32 +188,38 @@ router_gemm_bn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------ normalise the x tiles (warps 2..9)
-    // Thread i owns the 16-byte pieces i, i + 256, ... of the BLOCK_M x 128-byte tile: row (i >> 3) + 32 j,
-    // position i & 7.  With the 128-byte swizzle position p of row r holds the features 8 * (p ^ (r & 7)) .. + 7 of
-    // the k-block, and r & 7 does not depend on j, so one thread always handles the same eight features.
-    const int xt = threadIdx.x - 64;
+    // Two groups of four warps take alternate k-blocks, so that two tiles are being normalised at any time (one
+    // group's load -> arithmetic -> store -> proxy fence -> arrive chain took about 600 cycles per k-block and was the
+    // pace of the whole kernel).  Thread i of a group owns the 16-byte pieces i, i + 128, ... of the BLOCK_M x
+    // 128-byte tile: row (i >> 3) + 16 j, position i & 7.  With the 128-byte swizzle position p of row r holds the
+    // features 8 * (p ^ (r & 7)) .. + 7 of the k-block, and r & 7 does not depend on j, so one thread always handles the
+    // same eight features.
+    constexpr int kGroupThreads = (kXformWarps / 2) * 32;
+    constexpr int kGroupPieces = BLOCK_M * 8 / kGroupThreads;
+    const int group = (warp - 2) / (kXformWarps / 2);
+    const int xt = threadIdx.x - 64 - group * kGroupThreads;
     const int feat0 = 8 * ((xt & 7) ^ ((xt >> 3) & 7));
     bool ok = true;
-    for (int kb = 0; kb < num_k_blocks; ++kb) {
+    for (int kb = group; kb < num_k_blocks; kb += 2) {
       const int s = kb % kStages;
-      ok = ok && ptx::mbar_wait_bounded(full_bar(s), (kb / kStages) & 1u, abort_flag);
       float mm[8], ss[8];
 #pragma unroll
       for (int i = 0; i < 8; i += 2) {
         const float4 v = *reinterpret_cast<const float4*>(&stats[kb * BLOCK_K + (i >> 1) * 16 + (feat0 >> 3) * 2]);
         mm[i] = v.x; ss[i] = v.y; mm[i + 1] = v.z; ss[i + 1] = v.w;
       }
+      ok = ok && ptx::mbar_wait_bounded(full_bar(s), (kb / kStages) & 1u, abort_flag);
       uint4* tile = reinterpret_cast<uint4*>(gen + s * STAGE_BYTES);
-      uint4 q[kPieces];
+      uint4 q[kGroupPieces];
 #pragma unroll
-      for (int j = 0; j < kPieces; ++j) q[j] = tile[xt + 256 * j];
+      for (int j = 0; j < kGroupPieces; ++j) q[j] = tile[xt + kGroupThreads * j];
 #pragma unroll
-      for (int j = 0; j < kPieces; ++j) {
+      for (int j = 0; j < kGroupPieces; ++j) {
         float f[8];
         unpack16<T>(q[j], f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = (f[i] - mm[i]) * ss[i];
-        tile[xt + 256 * j] = pack16<T>(f);
+        tile[xt + kGroupThreads * j] = pack16<T>(f);
       }
       fence_async_smem();
       __syncwarp();
@@ -226,7 +265,7 @@ int launch_bn_gemm(const void* x, const void* w, const float* mean, const float*
   if ((rc = make_map(&tA, x, dtype, K, M, BLOCK_M)) != FMOE_OK) return rc;
   if ((rc = make_map(&tB, w, dtype, K, N, BLOCK_N)) != FMOE_OK) return rc;
   const int num_k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-  constexpr int kStages = RingDepth<BLOCK_N>::v;
+  constexpr int kStages = RingDepth<BLOCK_M, BLOCK_N>::v;
   const int smem = kStages * (BLOCK_M * BLOCK_K * 2 + BLOCK_N * BLOCK_K * 2) + (3 * kStages + 1) * 8 + 24 + num_k_blocks * BLOCK_K * 8 + 1024;
   auto kern = router_gemm_bn_kernel<BLOCK_M, BLOCK_N, T>;
   FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -260,7 +299,8 @@ int launch_router_bn_gemm(const void* x, const void* w, const float* mean, const
   const int64_t tiles128 = m_tiles * ((N + 127) / 128);
   const bool wide = N > 128 && tiles128 >= 4 * static_cast<int64_t>(device_sm_count());
   // fewer 128 x 128 tiles than SMs: 64-row tiles put twice as many CTAs to work, each with half the x tile
-  const bool small = tiles128 < device_sm_count();
+  bool small = tiles128 < device_sm_count();
+  if (const char* e = std::getenv("FMOE_BN_TILE")) small = e[0] == '6';  // measurement aid: 64 or 128 rows
 #define FMOE_BN_GEMM(BM_, BN_)                                                                                       \
   (dtype == FMOE_DTYPE_BF16                                                                                          \
        ? launch_bn_gemm<BM_, BN_, __nv_bfloat16>(x, w, mean, invstd, running_mean, running_var, eps, logits, dtype, M, N, \
