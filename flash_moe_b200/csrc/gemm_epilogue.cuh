@@ -11,34 +11,37 @@ namespace epi {
 
 // out[row, col_base .. col_base + NCOLS) = T(acc + addend + residual): float32 sum, one rounding.
 // taddr: TMEM address of the row's first column; arow (nullable): float32 addend row; rrow (nullable): residual row
-// in the module dtype; columns at or beyond n_valid are skipped (n_valid is a multiple of 8).  The addend and the
-// residual of the next 32 columns are fetched while the current 32 are converted and stored.
-template <typename T, int NCOLS>
-__device__ __forceinline__ void store_add_row(uint32_t taddr, T* orow, const float* arow, const T* rrow, int col_base,
-                                              int n_valid, bool row_ok) {
+// in the module dtype; columns at or beyond n_valid are skipped (n_valid is a multiple of 8).
+// The addend and the residual travel two 32-column chunks ahead of the chunk being converted and stored, and the
+// first two chunks are requested BEFORE `wait_accumulator()` is called (the caller's wait for the tile's last MMA):
+// timestamps taken inside the down GEMM showed the epilogue warps, one per scheduler and idle through the main loop,
+// spending ~2250 cycles per chunk when the operands were requested only one chunk ahead and only after the wait -
+// a full L2 round trip each, 18 000 cycles for a 128 x 256 tile.  `wait_accumulator` returns false to give up.
+template <typename T, int NCOLS, typename WaitFn>
+__device__ __forceinline__ bool store_add_row(uint32_t taddr, T* orow, const float* arow, const T* rrow, int col_base,
+                                              int n_valid, bool row_ok, WaitFn&& wait_accumulator) {
   constexpr int NCHUNK = NCOLS / 32;
-  float4 nxt[8];
-  uint4 rnxt[4];
-  auto fetch = [&](int c) {
+  constexpr int DEPTH = 3;
+  float4 ad[DEPTH][8];
+  uint4 rs[DEPTH][4];
+  auto fetch = [&](int c, float4 (&a)[8], uint4 (&r)[4]) {
     const int col0 = col_base + c * 32;
 #pragma unroll
     for (int v = 0; v < 8; ++v)
-      nxt[v] = (arow != nullptr && col0 + v * 4 < n_valid) ? __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 4))
-                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+      a[v] = (arow != nullptr && col0 + v * 4 < n_valid) ? __ldg(reinterpret_cast<const float4*>(arow + col0 + v * 4))
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int v = 0; v < 4; ++v)
-      rnxt[v] = (rrow != nullptr && col0 + v * 8 < n_valid) ? ldg16(rrow + col0 + v * 8) : make_uint4(0, 0, 0, 0);
+      r[v] = (rrow != nullptr && col0 + v * 8 < n_valid) ? ldg16(rrow + col0 + v * 8) : make_uint4(0, 0, 0, 0);
   };
-  fetch(0);
-#pragma unroll 1
-  for (int c = 0; c < NCHUNK; ++c) {
-    float4 cur[8];
-    uint4 rcur[4];
+  fetch(0, ad[0], rs[0]);
+  if (NCHUNK > 1) fetch(1, ad[1], rs[1]);
+  if (!wait_accumulator()) return false;
 #pragma unroll
-    for (int v = 0; v < 8; ++v) cur[v] = nxt[v];
-#pragma unroll
-    for (int v = 0; v < 4; ++v) rcur[v] = rnxt[v];
-    if (c + 1 < NCHUNK) fetch(c + 1);
+  for (int c = 0; c < NCHUNK; ++c) {  // fully unrolled: the buffer a chunk uses is a compile-time choice
+    if (c + 2 < NCHUNK) fetch(c + 2, ad[(c + 2) % DEPTH], rs[(c + 2) % DEPTH]);
+    const float4 (&cur)[8] = ad[c % DEPTH];
+    const uint4 (&rcur)[4] = rs[c % DEPTH];
     uint32_t a[32];
     ptx::tmem_ld_32x32(taddr + c * 32, a);
     ptx::tmem_ld_wait();
@@ -62,6 +65,13 @@ __device__ __forceinline__ void store_add_row(uint32_t taddr, T* orow, const flo
       }
     }
   }
+  return true;
+}
+// the same for a caller that has already waited for the accumulator
+template <typename T, int NCOLS>
+__device__ __forceinline__ void store_add_row(uint32_t taddr, T* orow, const float* arow, const T* rrow, int col_base,
+                                              int n_valid, bool row_ok) {
+  (void)store_add_row<T, NCOLS>(taddr, orow, arow, rrow, col_base, n_valid, row_ok, [] { return true; });
 }
 
 // The accumulator holds NCOLS / 2 gate columns followed by NCOLS / 2 up columns of the same outputs:

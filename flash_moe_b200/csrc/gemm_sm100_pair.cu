@@ -173,24 +173,32 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int n_tile = tile / num_m_tiles;
       const int acc = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
-      bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), aph, abort_flag);
-      ok = __all_sync(kFull, ok);
-      if (!ok) break;
-      ptx::tc_fence_after();
-      if (tile + npairs >= num_tiles) pdl_launch_dependents();  // last tile: only this epilogue is left
+      // the tile's accumulator is complete when the leader's last commit lands; the ADD epilogue calls this AFTER it
+      // has requested its first addend and residual chunks, so that they travel during the end of the main loop
+      auto wait_accumulator = [&]() {
+        bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), aph, abort_flag);
+        ok = __all_sync(kFull, ok);
+        if (ok) {
+          ptx::tc_fence_after();
+          if (tile + npairs >= num_tiles) pdl_launch_dependents();  // last tile: only this epilogue is left
+        }
+        return ok;
+      };
       const uint32_t taddr = tmem_base + acc * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16);
       const int64_t row = static_cast<int64_t>(m_tile) * (2 * BLOCK_M) + rank * BLOCK_M + row_in_tile;
       const bool row_ok = row < M;
 
       T* orow = static_cast<T*>(ep.out) + row * ep.ldo;
       if constexpr (EPI == PAIR_EPI_SWIGLU) {
+        if (!wait_accumulator()) break;
         T* grow = ep.pre_gate != nullptr ? static_cast<T*>(ep.pre_gate) + row * ep.ldo : nullptr;
         T* urow = ep.pre_up != nullptr ? static_cast<T*>(ep.pre_up) + row * ep.ldo : nullptr;
         epi::store_swiglu_row<T, BLOCK_N>(taddr, orow, grow, urow, n_tile * (BLOCK_N / 2), ep.n_valid, row_ok);
       } else {
         const float* arow = (ep.addend != nullptr && row_ok) ? ep.addend + row * ep.ldo : nullptr;
         const T* rrow = (ep.residual != nullptr && row_ok) ? static_cast<const T*>(ep.residual) + row * ep.ldo : nullptr;
-        epi::store_add_row<T, BLOCK_N>(taddr, orow, arow, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok);
+        if (!epi::store_add_row<T, BLOCK_N>(taddr, orow, arow, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok, wait_accumulator))
+          break;
       }
       ptx::tc_fence_before();
       __syncwarp();
