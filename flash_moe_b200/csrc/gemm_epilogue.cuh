@@ -74,6 +74,38 @@ __device__ __forceinline__ void store_add_row(uint32_t taddr, T* orow, const flo
   (void)store_add_row<T, NCOLS>(taddr, orow, arow, rrow, col_base, n_valid, row_ok, [] { return true; });
 }
 
+// One 32-column chunk of the ADD epilogue with the float32 addend already in shared memory: `achunk` is a
+// [rows x 32] float32 box written by TMA with the 128-byte swizzle (16-byte piece j of row r sits at piece
+// j ^ (r & 7)), `srow` this thread's row inside it.  Same sums in the same order as store_add_row.
+template <typename T>
+__device__ __forceinline__ void store_add_chunk_smem(uint32_t taddr_chunk, T* orow, const uint8_t* achunk, int srow,
+                                                     const uint4 (&rcur)[4], bool has_residual, int col0, int n_valid,
+                                                     bool row_ok) {
+  uint32_t a[32];
+  ptx::tmem_ld_32x32(taddr_chunk, a);
+  ptx::tmem_ld_wait();
+  if (!row_ok) return;
+  const uint8_t* rowp = achunk + srow * 128;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (col0 + v * 8 < n_valid) {
+      const float4 c0 = *reinterpret_cast<const float4*>(rowp + (((2 * v) ^ (srow & 7)) << 4));
+      const float4 c1 = *reinterpret_cast<const float4*>(rowp + (((2 * v + 1) ^ (srow & 7)) << 4));
+      float f[8], r[8];
+      unpack16<T>(rcur[v], r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
+      f[0] += c0.x; f[1] += c0.y; f[2] += c0.z; f[3] += c0.w;
+      f[4] += c1.x; f[5] += c1.y; f[6] += c1.z; f[7] += c1.w;
+      if (has_residual) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += r[i];
+      }
+      *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
+    }
+  }
+}
+
 // The accumulator holds NCOLS / 2 gate columns followed by NCOLS / 2 up columns of the same outputs:
 // out[row, col_base .. col_base + NCOLS / 2) = T(silu(gate) * up); grow / urow (nullable, both or neither) receive
 // the two pre-activations rounded to T.
@@ -145,6 +177,22 @@ inline int make_tensor_map(CUtensorMap* m, const void* basep, int dtype, uint64_
   const CUtensorMapDataType dt = dtype == FMOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = fn(m, dt, 2, const_cast<void*>(basep), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FMOE_OK : FMOE_ERR_BAD_ARG;
+}
+
+// float32 [rows, cols] row-major, boxes of 32 columns (128 bytes) x box_rows rows, 128-byte swizzle: the addend tile of
+// the down GEMM's epilogue
+inline int make_tensor_map_f32(CUtensorMap* m, const void* basep, uint64_t cols, uint64_t rows, uint64_t pitch,
+                               uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return -static_cast<int>(cudaErrorNotSupported);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch * 4};
+  const cuuint32_t box[2] = {32, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(basep), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FMOE_OK : FMOE_ERR_BAD_ARG;
 }

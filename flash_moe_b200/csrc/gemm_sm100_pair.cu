@@ -33,7 +33,11 @@ constexpr int B_BYTES = (BLOCK_N / 2) * BLOCK_K * 2;  // this CTA's half of the 
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // 32 KB
 constexpr int STAGES = 6;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+constexpr int ADDEND_CHUNK_BYTES = BLOCK_M * 32 * 4;  // this CTA's 128 rows x 32 float32 columns of the addend
+constexpr int ADDEND_BUFS = 2;  // four (with a five-stage ring) measured the same: 35.4 vs 35.8 us
+constexpr int ADDEND_BYTES = ADDEND_BUFS * ADDEND_CHUNK_BYTES;  // chunks on their way while one is being added
+constexpr int SMEM_BYTES = RING_BYTES + ADDEND_BYTES + 256 + 1024;
 
 enum { PAIR_EPI_ADD = 0, PAIR_EPI_SWIGLU = 1 };
 
@@ -58,15 +62,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw_u32);
-  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = base + RING_BYTES + ADDEND_BYTES;
   auto a_smem = [&](int s) { return base + s * STAGE_BYTES; };
   auto b_smem = [&](int s) { return base + s * STAGE_BYTES + A_BYTES; };
   auto full_bar = [&](int s) { return bar_base + s * 8; };
   auto empty_bar = [&](int s) { return bar_base + (STAGES + s) * 8; };
   auto tfull_bar = [&](int a) { return bar_base + (2 * STAGES + a) * 8; };
   auto tempty_bar = [&](int a) { return bar_base + (2 * STAGES + 2 + a) * 8; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 8);
+  auto cfull_bar = [&](int b) { return bar_base + (2 * STAGES + 4 + b) * 8; };  // addend chunk b has landed
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + RING_BYTES + ADDEND_BYTES + (2 * STAGES + 4 + ADDEND_BUFS) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + RING_BYTES + ADDEND_BYTES + (2 * STAGES + 4 + ADDEND_BUFS) * 8 + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -84,11 +89,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 8);  // leader only is used: 4 epilogue warps of each CTA
     }
+    for (int b = 0; b < ADDEND_BUFS; ++b) ptx::mbar_init(cfull_bar(b), 1);
     *abort_flag = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB0);
-    if (EPI == PAIR_EPI_SWIGLU) ptx::prefetch_tensormap(&tmB1);
+    if (EPI == PAIR_EPI_SWIGLU || ep.addend != nullptr) ptx::prefetch_tensormap(&tmB1);  // ADD: the addend's map
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -195,10 +201,54 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         T* urow = ep.pre_up != nullptr ? static_cast<T*>(ep.pre_up) + row * ep.ldo : nullptr;
         epi::store_swiglu_row<T, BLOCK_N>(taddr, orow, grow, urow, n_tile * (BLOCK_N / 2), ep.n_valid, row_ok);
       } else {
-        const float* arow = (ep.addend != nullptr && row_ok) ? ep.addend + row * ep.ldo : nullptr;
         const T* rrow = (ep.residual != nullptr && row_ok) ? static_cast<const T*>(ep.residual) + row * ep.ldo : nullptr;
-        if (!epi::store_add_row<T, BLOCK_N>(taddr, orow, arow, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok, wait_accumulator))
-          break;
+        if (ep.addend == nullptr) {
+          if (!epi::store_add_row<T, BLOCK_N>(taddr, orow, nullptr, rrow, n_tile * BLOCK_N, ep.n_valid, row_ok, wait_accumulator))
+            break;
+        } else {
+          // The float32 addend comes through shared memory: one thread asks TMA for this CTA's 128 rows x 32 columns
+          // of it, two chunks ahead (the first two before the accumulator is complete), and every thread reads its
+          // own row from the swizzled box.  Fetched one row per thread from global memory, 16 bytes per access, the
+          // addend cost 6 us of the 37 (measured by taking the loads out); tmB1 carries its tensor map here.
+          constexpr int NCHUNK = BLOCK_N / 32;
+          const int a_row0 = m_tile * (2 * BLOCK_M) + static_cast<int>(rank) * BLOCK_M;
+          auto request = [&](int c) {  // by thread 64 only
+            const int b = c % ADDEND_BUFS;
+            ptx::mbar_arrive_expect_tx(cfull_bar(b), ADDEND_CHUNK_BYTES);
+            ptx::tma_load_2d(base + RING_BYTES + b * ADDEND_CHUNK_BYTES, &tmB1, cfull_bar(b), n_tile * BLOCK_N + c * 32, a_row0);
+          };
+          if (threadIdx.x == 64) {
+#pragma unroll
+            for (int c = 0; c < ADDEND_BUFS; ++c) request(c);
+          }
+          // every warp walks all chunks and meets the others at the barrier even after a wait has given up (the
+          // waits then return at once: the abort flag is up), so that the named barrier can never be left hanging
+          bool cok = wait_accumulator();
+          int requested = ADDEND_BUFS;
+#pragma unroll 1
+          for (int c = 0; c < NCHUNK; ++c) {
+            const int b = c % ADDEND_BUFS;
+            const uint32_t cph = (tcount * (NCHUNK / ADDEND_BUFS) + c / ADDEND_BUFS) & 1u;  // uses of buffer b so far
+            if (c < requested) cok = ptx::mbar_wait_bounded(cfull_bar(b), cph, abort_flag) && cok;
+            else cok = false;
+            cok = __all_sync(kFull, cok);
+            uint4 rcur[4];
+            const int col0 = n_tile * BLOCK_N + c * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              rcur[v] = (rrow != nullptr && col0 + v * 8 < ep.n_valid) ? ldg16(rrow + col0 + v * 8) : make_uint4(0, 0, 0, 0);
+            if (cok)
+              epi::store_add_chunk_smem<T>(taddr + c * 32, orow, gen + RING_BYTES + b * ADDEND_CHUNK_BYTES, row_in_tile, rcur,
+                                           rrow != nullptr, col0, ep.n_valid, row_ok);
+            // all four epilogue warps are done with buffer b before it is refilled
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (c + ADDEND_BUFS < NCHUNK && *abort_flag == 0) {
+              if (threadIdx.x == 64) request(c + ADDEND_BUFS);
+              requested = c + ADDEND_BUFS + 1;
+            }
+          }
+          if (!__all_sync(kFull, cok)) break;
+        }
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -266,9 +316,11 @@ int launch_gemm_add_pair(const void* a, const void* b, const float* addend, void
   if ((rc = make_map(&tB, b, dtype, K, N, BLOCK_N / 2)) != FMOE_OK) return rc;
   PairEpi ep{out, addend, residual, N, N, nullptr, nullptr};
   const int n_tiles = (N + 255) / 256;
+  CUtensorMap tC = tB;  // third slot: the float32 addend's map (unused without an addend)
+  if (addend != nullptr && (rc = epi::make_tensor_map_f32(&tC, addend, N, M, N, BLOCK_M)) != FMOE_OK) return rc;
   if (dtype == FMOE_DTYPE_BF16)
-    return launch_pair<PAIR_EPI_ADD, __nv_bfloat16>(tA, tB, tB, ep, M, n_tiles, K, status, stream);
-  return launch_pair<PAIR_EPI_ADD, __half>(tA, tB, tB, ep, M, n_tiles, K, status, stream);
+    return launch_pair<PAIR_EPI_ADD, __nv_bfloat16>(tA, tB, tC, ep, M, n_tiles, K, status, stream);
+  return launch_pair<PAIR_EPI_ADD, __half>(tA, tB, tC, ep, M, n_tiles, K, status, stream);
 }
 
 }  // namespace fmoe
