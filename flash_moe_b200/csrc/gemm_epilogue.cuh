@@ -86,22 +86,35 @@ __device__ __forceinline__ void store_add_chunk_smem(uint32_t taddr_chunk, T* or
   ptx::tmem_ld_wait();
   if (!row_ok) return;
   const uint8_t* rowp = achunk + srow * 128;
+  uint4 pk[4];
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
-    if (col0 + v * 8 < n_valid) {
-      const float4 c0 = *reinterpret_cast<const float4*>(rowp + (((2 * v) ^ (srow & 7)) << 4));
-      const float4 c1 = *reinterpret_cast<const float4*>(rowp + (((2 * v + 1) ^ (srow & 7)) << 4));
-      float f[8], r[8];
-      unpack16<T>(rcur[v], r);
+    const float4 c0 = *reinterpret_cast<const float4*>(rowp + (((2 * v) ^ (srow & 7)) << 4));
+    const float4 c1 = *reinterpret_cast<const float4*>(rowp + (((2 * v + 1) ^ (srow & 7)) << 4));
+    float f[8], r[8];
+    unpack16<T>(rcur[v], r);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
-      f[0] += c0.x; f[1] += c0.y; f[2] += c0.z; f[3] += c0.w;
-      f[4] += c1.x; f[5] += c1.y; f[6] += c1.z; f[7] += c1.w;
-      if (has_residual) {
+    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[v * 8 + i]);
+    f[0] += c0.x; f[1] += c0.y; f[2] += c0.z; f[3] += c0.w;
+    f[4] += c1.x; f[5] += c1.y; f[6] += c1.z; f[7] += c1.w;
+    if (has_residual) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] += r[i];
-      }
-      *reinterpret_cast<uint4*>(orow + col0 + v * 8) = pack16<T>(f);
+      for (int i = 0; i < 8; ++i) f[i] += r[i];
+    }
+    pk[v] = pack16<T>(f);
+  }
+  // 32-byte stores (one whole sector per instruction) where the row is 32-byte aligned, 16-byte stores otherwise
+  T* dst = orow + col0;
+  const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
+#pragma unroll
+  for (int v = 0; v < 4; v += 2) {
+    if (wide && col0 + v * 8 + 8 < n_valid) {
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + v * 8), "r"(pk[v].x), "r"(pk[v].y),
+                   "r"(pk[v].z), "r"(pk[v].w), "r"(pk[v + 1].x), "r"(pk[v + 1].y), "r"(pk[v + 1].z), "r"(pk[v + 1].w)
+                   : "memory");
+    } else {
+      if (col0 + v * 8 < n_valid) *reinterpret_cast<uint4*>(dst + v * 8) = pk[v];
+      if (col0 + v * 8 + 8 < n_valid) *reinterpret_cast<uint4*>(dst + v * 8 + 8) = pk[v + 1];
     }
   }
 }
