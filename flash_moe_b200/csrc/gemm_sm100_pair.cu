@@ -247,7 +247,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               requested = c + ADDEND_BUFS + 1;
             }
           }
-          if (!__all_sync(kFull, cok)) break;
+          if (!__all_sync(kFull, cok)) {
+            // gave up: let the addend boxes already requested land before this CTA's shared memory goes away (bounded)
+            if (threadIdx.x == 64) {
+              for (int c = requested - ADDEND_BUFS > 0 ? requested - ADDEND_BUFS : 0; c < requested && c < NCHUNK; ++c)
+                ptx::mbar_wait_drain(cfull_bar(c % ADDEND_BUFS), (tcount * (NCHUNK / ADDEND_BUFS) + c / ADDEND_BUFS) & 1u);
+            }
+            break;
+          }
         }
       }
       ptx::tc_fence_before();
